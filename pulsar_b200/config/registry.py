@@ -2,7 +2,7 @@
 
 The reference picks its model class by a prefix of a caller-supplied string
 (pulsar-core/src/runtime/engine.cpp:43-84).  Here the name comes from
-``config.json`` (``architectures[0]``, else ``model_type``), and every registry is
+``config.json`` (``architectures[0]``, else ``model_type``, else ``architecture``), and every registry is
 open: a test or a user registers a new architecture, mixer, feed-forward, norm,
 position encoding or block arrangement without touching the package.
 """
@@ -55,7 +55,9 @@ def architecture_name(raw: Dict[str, Any]) -> str:
         return str(archs[0])
     if raw.get("model_type"):
         return str(raw["model_type"])
-    raise ConfigError("config.json: neither 'architectures' nor 'model_type' names the model")
+    if isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
+    raise ConfigError("config.json: neither 'architectures', 'model_type' nor 'architecture' names the model")
 
 
 def config_from_dict(raw: Dict[str, Any]):

@@ -16,6 +16,7 @@ class NormSpec:
     kind: str            # "rmsnorm"
     size: int
     eps: float
+    suffix: str = "weight"   # the weight's tensor name is the part's prefix + this ("" where the prefix is the whole name)
 
 
 @dataclass(frozen=True)
@@ -40,10 +41,21 @@ class MixerSpec:
     qk_norm_eps: Optional[float] = None   # None: no per-head q/k norm
     position: Optional[PositionSpec] = None
     own_kv: bool = True              # False: attends over another layer's cache, has no k/v projection
+    v_head_dim: int = 0              # width of a value head; 0: head_dim
+    chunk: Optional[int] = None      # c: a query at p sees only keys j with floor(j / c) == floor(p / c), chunks counted from 0
+    distance_bias: Optional[float] = None   # r: the score loses 2^(-r (h+1) / n_heads) * (p - j) for head h; None: no bias
+    tensor_names: Tuple[Tuple[str, str], ...] = ()   # role ("q", "k", "v", "o", ...) -> name behind the prefix, where not the default
     extra: Tuple[Tuple[str, object], ...] = ()   # free-form parameters of other kinds
 
     def option(self, name, default=None):
         return dict(self.extra).get(name, default)
+
+    def tensor_name(self, role: str, default: str) -> str:
+        return dict(self.tensor_names).get(role, default)
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -60,14 +72,18 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class BlockSpec:
-    """Arrangement of one layer.  ``kind`` "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x))."""
+    """Arrangement of one layer.  ``kind`` "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x)).
+    ``kind`` "sandwich": x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x))), the second sublayer only where
+    ``feed_forward`` is given."""
     kind: str
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]
     mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
     weight_prefix: str                      # e.g. "model.layers.3."
-    names: Tuple[Tuple[str, str], ...] = ()  # sub-prefixes: mixer, feed_forward, mixer_norm, feed_forward_norm
+    names: Tuple[Tuple[str, str], ...] = ()  # sub-prefixes: mixer, feed_forward, mixer_norm, feed_forward_norm (+ the post norms)
+    mixer_post_norm: Optional[NormSpec] = None          # norm of the mixer's output before it joins the stream
+    feed_forward_post_norm: Optional[NormSpec] = None   # the same behind the feed-forward
 
     def sub_prefix(self, part: str) -> str:
         return self.weight_prefix + dict(self.names)[part]

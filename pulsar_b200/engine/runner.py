@@ -83,6 +83,9 @@ class ModelRunner:
         # gained (a few hundred bytes for a decode step instead of the whole [sequences, width] table).
         # PULSAR_RESIDENT_TABLES=0: every step brings whole tables.
         self.resident_tables = os.environ.get("PULSAR_RESIDENT_TABLES", "1") != "0"
+        # For looking inside a step: called as layer_hook(index in the run order, residual, pending delta) behind every
+        # layer call (the stream is residual + delta where a delta is pending).  A step with a hook is never captured.
+        self.layer_hook = None
         cache.set_resident_tables(self.resident_tables)
 
     # ------------------------------------------------------------------ memory
@@ -191,6 +194,7 @@ class ModelRunner:
         kv_lens = [st + q for st, q in zip(starts, q_lens)]
         host_batch = HostBatch(q_lens, kv_lens, state_slots)
         ctx = StepContext(self, n, s, host_batch)
+        ctx.on_layer = self.layer_hook
         widths = list(widths_c[:n_groups])
         ctx.table_widths = tuple(widths)
         moved = any(e.token_src is not None for e in entries)
@@ -266,7 +270,7 @@ class ModelRunner:
         return logits
 
     def _forward(self, ctx: StepContext) -> torch.Tensor:
-        if not (self.cuda_graphs and ctx.all_decode) or self.position_axes > 1:
+        if not (self.cuda_graphs and ctx.all_decode) or self.position_axes > 1 or ctx.on_layer is not None:
             return self.model.forward(ctx)
         if self._graph_epoch != self.scratch_epoch:       # a buffer moved: every captured address is stale
             self._graphs.clear()

@@ -13,6 +13,12 @@ from ..config.specs import ModelSpec
 from ..parts.base import Part, StepContext, WeightSpec
 
 
+def _without(name: str, suffix: str) -> str:
+    if suffix and not name.endswith(suffix):
+        raise ValueError(f"the final norm's tensor '{name}' does not end in its suffix '{suffix}'")
+    return name[: len(name) - len(suffix)]
+
+
 class DecoderModel(Part):
     """embedding -> the blocks in ``run_order`` -> final norm at the wanted rows -> head
     (pulsar-core/src/model/paged_forward.cpp:82-94; pulsar-core/src/model/qwen3.cpp:123-129).
@@ -31,7 +37,7 @@ class DecoderModel(Part):
             raise ValueError("logit_softcap must be positive")
         self.spec, self.dtype = spec, dtype
         self.blocks = [BLOCKS.get(b.kind)(b, dtype) for b in spec.blocks]
-        self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, spec.final_norm_name[: -len("weight")], dtype,
+        self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, _without(spec.final_norm_name, spec.final_norm.suffix), dtype,
                                                           "norm.final")
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
@@ -105,6 +111,8 @@ class DecoderModel(Part):
             following = self.blocks[s.run_order[i + 1].block] if i + 1 < len(s.run_order) else None
             ctx.next_norm = getattr(following, "mixer_norm", None)
             delta = self.blocks[call.block].forward(ctx, residual, delta, ctx.cache(call.cache))
+            if ctx.on_layer is not None:
+                ctx.on_layer(i, residual, delta)
         rows = ctx.logit_rows
         logits = ctx.scratch("logits", (rows.numel(), s.vocab_size), torch.float32)
         if rows.numel():

@@ -37,7 +37,7 @@ torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 _ERRORS = {-2: "unsupported dtype", -3: "unsupported size or argument", -4: "size exceeds the kernel's limit"}
 
-_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_long
 _SIGNATURES = {
     "pb_embed": [_I, _P, _P, _P, _I, _I, _I, _F, _P],
     "pb_scale_cap": [_P, ctypes.c_longlong, _F, _F, _P],
@@ -83,6 +83,14 @@ _SIGNATURES = {
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P],
     "pb_sample_workspace": [_I],
     "pb_argmax": [_P, _I, _I, _P, _P, _P],
+    "pb_paged_attention_general": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "pb_qkv_split_write": [_I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "pb_heads_linear": [_I, _I, _P, _L, _I, _P, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
+    "pb_latent_prepare": [_I, _P, _L, _P, _L, _P, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "pb_causal_conv_silu": [_I, _P, _L, _P, _P, _P, _L, _L, _P, _P, _P, _P, _I, _I, _I, _P],
+    "pb_selective_scan": [_I, _P, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "pb_post_norm_add": [_I, _P, _P, _P, _F, _P, _F, _P, _I, _I, _P],
+    "pb_clamped_glu": [_I, _P, _P, _I, _I, _F, _F, _P],
 }
 _fns = {}
 # the entry points that launch kernels (the others answer questions on the host): what PULSAR_PROF=1 times
@@ -90,7 +98,9 @@ _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk
               "paged_attention_generic", "paged_attention_decode", "paged_attention_decode_tc", "paged_attention_decode_tc_fused",
               "paged_attention_decode_tc_qkv",
               "paged_attention_prefill_tc", "paged_attention_prefill_tcgen05", "gemm_skinny", "gemm_skinny_accumulate",
-              "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update"}
+              "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update",
+              "paged_attention_general", "qkv_split_write", "heads_linear", "latent_prepare", "causal_conv_silu",
+              "selective_scan", "post_norm_add", "clamped_glu"}
 
 
 class KernelError(RuntimeError):
@@ -862,3 +872,146 @@ def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, wind
         return
     paged_attention_generic(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
                             ctx.seq_of_token, scale, window)
+
+
+# ---------------------------------------------------------------- attention in its general form, latent attention
+def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                            block_table: torch.Tensor, scale: float, window: Optional[int] = None, chunk: Optional[int] = None,
+                            slopes: Optional[torch.Tensor] = None, key_width: Optional[int] = None,
+                            value_width: Optional[int] = None) -> None:
+    """Attention of the step's tokens (``ctx``: cu_q, kv_len, seq_of_token) with float32 queries ``q`` [N, Hq, Dk]
+    over pools [pages, Hkv, page, stride]: keys are the first ``key_width`` (default: all) elements of a ``k_pool``
+    row, values the first ``value_width`` of a ``v_pool`` row (the two may be one tensor).  ``slopes`` [Hq] float32:
+    the score loses slopes[h] * distance.  ``window`` / ``chunk`` bound the visible keys from below."""
+    _cuda(q, k_pool, v_pool, out, block_table, slopes)
+    _check_against(k_pool)
+    n, hq, dk = q.shape
+    pages, hkv, page_size, k_stride = k_pool.shape
+    v_stride = v_pool.shape[3]
+    dv = out.shape[2]
+    assert q.dtype == torch.float32 and k_pool.dtype == v_pool.dtype == out.dtype and out.shape[:2] == (n, hq)
+    assert (key_width or k_stride) == dk and (value_width or v_stride) == dv and v_pool.shape[:3] == k_pool.shape[:3]
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == hq)
+    check(fn("pb_paged_attention_general")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
+                                           block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len), _p(ctx.seq_of_token), _p(slopes),
+                                           n, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale), int(window or 0),
+                                           int(chunk or 0), stream()), "paged_attention_general")
+
+
+def qkv_split_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                    slots: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int,
+                    page_size: int) -> None:
+    """Split the fused projection rows [q: Hq*Dk | k: Hkv*Dk | v: Hkv*Dv]: queries to float32 ``q_out`` [N, Hq, Dk], keys and
+    values into their pages (``n_kv_heads`` 0: the row holds q only)."""
+    _cuda(qkv, q_out, k_pool, v_pool, slots)
+    _check_against(k_pool)
+    n = qkv.shape[0]
+    assert qkv.shape[1] == n_heads * key_dim + n_kv_heads * (key_dim + value_dim) and q_out.dtype == torch.float32
+    assert q_out.shape == (n, n_heads, key_dim)
+    if n_kv_heads:
+        assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype and slots.dtype == torch.int32
+        assert k_pool.shape[1:] == (n_kv_heads, page_size, key_dim) and v_pool.shape[1:] == (n_kv_heads, page_size, value_dim)
+    check(fn("pb_qkv_split_write")(code(qkv.dtype), _p(qkv), _p(q_out), _p(k_pool), _p(v_pool), _p(slots), n, n_heads, n_kv_heads,
+                                   key_dim, value_dim, page_size, stream()), "qkv_split_write")
+
+
+def heads_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+    """out[n, h, :] = w[h] @ a[n, h, :] for every head (float32 sums in ascending k), times sigmoid(gate[n, h, :]) where a
+    gate is given.  ``a`` [N, H, K], ``out`` [N, H, M] and ``gate`` [N, H * M] may be views whose last dimension is
+    contiguous; ``w`` [H, M, K] is contiguous.  ``out`` is float32 or of the dtype of ``a`` and ``w``."""
+    n, h, k = a.shape
+    h2, m, k2 = w.shape
+    assert (h2, k2) == (h, k) and out.shape == (n, h, m) and a.dtype == w.dtype and w.is_contiguous()
+    assert a.is_cuda and w.is_cuda and out.is_cuda and a.stride(2) == 1 and out.stride(2) == 1
+    g_tok = 0
+    if gate is not None:
+        assert gate.dtype == a.dtype and gate.shape == (n, h * m) and gate.stride(1) == 1 and gate.is_cuda
+        g_tok = gate.stride(0)
+    check(fn("pb_heads_linear")(code(a.dtype), code(out.dtype), _p(a), a.stride(0), a.stride(1), _p(w), _p(out), out.stride(0),
+                                out.stride(1), _p(gate), g_tok, n, h, m, k, stream()), "heads_linear")
+
+
+def latent_prepare(q: torch.Tensor, down: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float,
+                   cos: torch.Tensor, sin: torch.Tensor, slots: Optional[torch.Tensor], pool: Optional[torch.Tensor],
+                   q_full: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, page_size: int) -> None:
+    """Per token: where ``down`` [N, rank + rot_dim] is given, its latent part RMS-normed with ``norm_weight`` and its
+    rotated part turned at the token's position go to the token's slot of ``pool`` [pages, 1, page, rank + rot_dim];
+    every head's rotated query part (behind ``dim`` plain dimensions of a ``q`` row) goes, turned, to the tail of
+    ``q_full`` float32 [N, H, rank + rot_dim].  ``q`` and ``down`` may be column slices of one tensor.  The rotation
+    pairs neighbours; ``cos`` / ``sin`` [N, rotated dims / 2]."""
+    n = q.shape[0]
+    assert q.is_cuda and q.stride(1) == 1 and q.shape[1] == n_heads * (dim + rot_dim)
+    assert q_full.dtype == torch.float32 and q_full.is_contiguous() and q_full.shape == (n, n_heads, rank + rot_dim)
+    assert cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[0] == n and cos.is_contiguous()
+    rot_dims = 2 * cos.shape[1]
+    down_tok = 0
+    if down is not None:
+        assert down.dtype == q.dtype and down.shape == (n, rank + rot_dim) and down.stride(1) == 1
+        assert norm_weight.dtype == torch.float32 and norm_weight.numel() == rank and slots.dtype == torch.int32
+        assert pool.dtype == q.dtype and pool.is_contiguous() and pool.shape[1:] == (1, page_size, rank + rot_dim)
+        _check_against(pool)
+        down_tok = down.stride(0)
+    check(fn("pb_latent_prepare")(code(q.dtype), _p(q), q.stride(0), _p(down), down_tok, _p(norm_weight), float(eps), _p(cos),
+                                  _p(sin), _p(slots), _p(pool), _p(q_full), n, n_heads, dim, rot_dim, rot_dims, rank, page_size,
+                                  stream()), "latent_prepare")
+
+
+# ---------------------------------------------------------------- selective scan
+def causal_conv_silu(ctx, xz: torch.Tensor, channels: int, taps: torch.Tensor, bias: torch.Tensor, arena: torch.Tensor,
+                     tail_offset: int, out: torch.Tensor) -> None:
+    """out [N, channels] = silu(causal convolution per channel) of the first ``channels`` columns of ``xz``; inputs before a
+    portion's start come from the sequence's slot of ``arena`` (float32 [slots, floats]; the tail [channels, taps - 1] at
+    ``tail_offset``).  ``taps`` float32 [channels, T], the last column weighs the current token."""
+    _cuda(xz, taps, bias, arena, out)
+    n = xz.shape[0]
+    assert taps.dtype == bias.dtype == arena.dtype == torch.float32 and taps.shape[0] == channels and bias.numel() == channels
+    assert out.shape == (n, channels) and out.dtype == xz.dtype and xz.shape[1] >= channels and arena.dim() == 2
+    check(fn("pb_causal_conv_silu")(code(xz.dtype), _p(xz), xz.shape[1], _p(taps), _p(bias), _p(arena), arena.shape[1],
+                                    int(tail_offset), _p(ctx.cu_q), _p(ctx.seq_of_token), _p(ctx.state_slots), _p(out), n, channels,
+                                    taps.shape[1], stream()), "causal_conv_silu")
+
+
+def selective_scan(ctx, x: torch.Tensor, xz: torch.Tensor, proj: torch.Tensor, w_dt: torch.Tensor, dt_bias: torch.Tensor,
+                   a_log: torch.Tensor, d_skip: torch.Tensor, arena: torch.Tensor, tail_offset: int, n_taps: int,
+                   out: torch.Tensor) -> None:
+    """The selective scan over the step's portions, token after token per sequence, with each sequence's state
+    [inner, state] (float32) in its slot of ``arena``; moves the slot's convolution tail on when a portion is done.
+    x [N, inner] convolution output, xz [N, 2 inner] the input projection (convolution inputs | gates), proj [N, dt_rank +
+    2 state] = [r | B | C], w_dt [inner, dt_rank]; out [N, inner] = (scan + d_skip * x) * silu(gate)."""
+    _cuda(x, xz, proj, w_dt, dt_bias, a_log, d_skip, arena, out)
+    n, inner = x.shape
+    n_state = a_log.shape[1]
+    dt_rank = w_dt.shape[1]
+    assert xz.shape == (n, 2 * inner) and proj.shape == (n, dt_rank + 2 * n_state) and w_dt.shape[0] == inner
+    assert x.dtype == xz.dtype == proj.dtype == w_dt.dtype == out.dtype and out.shape == (n, inner)
+    assert dt_bias.dtype == a_log.dtype == d_skip.dtype == arena.dtype == torch.float32 and a_log.shape[0] == inner
+    assert arena.dim() == 2 and arena.shape[1] >= tail_offset + inner * (n_taps - 1) and tail_offset >= inner * n_state
+    check(fn("pb_selective_scan")(code(x.dtype), _p(x), _p(xz), xz.shape[1], _p(proj), proj.shape[1], _p(w_dt), _p(dt_bias),
+                                  _p(a_log), _p(d_skip), _p(arena), arena.shape[1], int(tail_offset), _p(out), _p(ctx.cu_q),
+                                  _p(ctx.state_slots), ctx.n_seqs, inner, n_state, dt_rank, int(n_taps), stream()),
+          "selective_scan")
+
+
+# ---------------------------------------------------------------- norms behind sublayers, clamped gating
+def post_norm_add(residual: torch.Tensor, delta: torch.Tensor, w_post: torch.Tensor, eps_post: float,
+                  w_next: Optional[torch.Tensor] = None, eps_next: float = 0.0, out: Optional[torch.Tensor] = None) -> None:
+    """residual (float32) += rmsnorm(delta) * w_post; with ``w_next`` also out = rmsnorm(residual) * w_next."""
+    _cuda(residual, delta, w_post, w_next, out)
+    n, width = residual.shape
+    assert residual.dtype == torch.float32 and delta.shape == residual.shape and w_post.dtype == torch.float32
+    assert w_post.numel() == width
+    if w_next is not None:
+        assert w_next.dtype == torch.float32 and w_next.numel() == width and out.shape == residual.shape and out.dtype == delta.dtype
+    check(fn("pb_post_norm_add")(code(delta.dtype), _p(residual), _p(delta), _p(w_post), float(eps_post), _p(w_next),
+                                 float(eps_next), _p(out), n, width, stream()), "post_norm_add")
+
+
+def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out [N, I] = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit);
+    ``gate_up`` [N, 2I] holds the gate columns, then the up columns."""
+    _cuda(gate_up, out)
+    n, two_i = gate_up.shape
+    assert two_i % 2 == 0 and out.shape == (n, two_i // 2) and out.dtype == gate_up.dtype
+    check(fn("pb_clamped_glu")(code(out.dtype), _p(gate_up), _p(out), n, two_i // 2, float(limit), float(alpha), stream()),
+          "clamped_glu")

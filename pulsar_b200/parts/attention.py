@@ -6,7 +6,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
-from ..cache.manager import CacheNeed
+from ..cache.manager import CachedTensor, CacheNeed
 from ..config.registry import MIXERS, POSITIONS
 from ..config.specs import MixerSpec
 from .base import CacheView, Mixer, StepContext, WeightSpec
@@ -23,67 +23,102 @@ class Attention(Mixer):
 
     Keys are stored rotated, once, at their absolute position.  With ``own_kv`` False the
     mixer has no k/v projection and attends over pages another layer wrote this step.
+
+    The general form (``self.general``: value heads of another width than the key heads, a chunk mask, or a
+    linear distance bias per head) has no rotation and no per-head norm; positions enter through the bias and
+    the masks alone.  Its queries stay float32 from the projection to the scores
+    (``ops.qkv_split_write`` / ``ops.paged_attention_general``).
     """
 
     def __init__(self, spec: MixerSpec, prefix: str, dtype: torch.dtype):
         if spec.n_heads <= 0 or spec.n_kv_heads <= 0 or spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"attention: {spec.n_heads} query heads cannot be grouped over {spec.n_kv_heads} kv heads")
-        if spec.head_dim % 16 or spec.head_dim > 256:
+        self.general = bool(spec.value_dim != spec.head_dim or spec.chunk is not None or spec.distance_bias is not None)
+        if self.general:
+            if spec.position is not None or spec.qk_norm_eps is not None:
+                raise ValueError("attention: the general form (value width, chunk mask, distance bias) has neither rotation nor q/k norm")
+            if spec.head_dim <= 0 or spec.value_dim <= 0 or (spec.chunk is not None and spec.chunk <= 0):
+                raise ValueError("attention: head sizes and the chunk size must be positive")
+        elif spec.head_dim % 16 or spec.head_dim > 256:
             raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16, at most 256")
         if spec.window is not None and spec.window <= 0:
             raise ValueError("attention: window must be positive")
         self.spec, self.prefix, self.dtype = spec, prefix, dtype
         self.position = POSITIONS.get(spec.position.kind)(spec.position) if spec.position is not None else None
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.slopes = None
+        name = spec.tensor_name
+        self.names = {"q": name("q", "q_proj.weight"), "k": name("k", "k_proj.weight"), "v": name("v", "v_proj.weight"),
+                      "o": name("o", "o_proj.weight"), "q_norm": name("q_norm", "q_norm.weight"),
+                      "k_norm": name("k_norm", "k_norm.weight")}
 
     # ---------------------------------------------------------------- weights
     def weight_specs(self) -> List[WeightSpec]:
-        s, p = self.spec, self.prefix
-        specs = [WeightSpec(p + "q_proj.weight", (s.n_heads * s.head_dim, s.hidden))]
+        s, p, nm = self.spec, self.prefix, self.names
+        specs = [WeightSpec(p + nm["q"], (s.n_heads * s.head_dim, s.hidden))]
         if s.own_kv:
-            specs += [WeightSpec(p + "k_proj.weight", (s.n_kv_heads * s.head_dim, s.hidden)),
-                      WeightSpec(p + "v_proj.weight", (s.n_kv_heads * s.head_dim, s.hidden))]
-        specs.append(WeightSpec(p + "o_proj.weight", (s.hidden, s.n_heads * s.head_dim)))
+            specs += [WeightSpec(p + nm["k"], (s.n_kv_heads * s.head_dim, s.hidden)),
+                      WeightSpec(p + nm["v"], (s.n_kv_heads * s.value_dim, s.hidden))]
+        specs.append(WeightSpec(p + nm["o"], (s.hidden, s.n_heads * s.value_dim)))
         if s.qk_norm_eps is not None:
-            specs.append(WeightSpec(p + "q_norm.weight", (s.head_dim,), role="vector", init="ones_normal"))
+            specs.append(WeightSpec(p + nm["q_norm"], (s.head_dim,), role="vector", init="ones_normal"))
             if s.own_kv:
-                specs.append(WeightSpec(p + "k_norm.weight", (s.head_dim,), role="vector", init="ones_normal"))
+                specs.append(WeightSpec(p + nm["k_norm"], (s.head_dim,), role="vector", init="ones_normal"))
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        s, p = self.spec, self.prefix
-        parts = [tensors[p + "q_proj.weight"]]
+        s, p, nm = self.spec, self.prefix, self.names
+        parts = [tensors[p + nm["q"]]]
         if s.own_kv:
-            parts += [tensors[p + "k_proj.weight"], tensors[p + "v_proj.weight"]]
+            parts += [tensors[p + nm["k"]], tensors[p + nm["v"]]]
         self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0]   # rows: q | k | v
-        self.w_o = tensors[p + "o_proj.weight"]
+        self.w_o = tensors[p + nm["o"]]
         if s.qk_norm_eps is not None:
-            self.q_norm = tensors[p + "q_norm.weight"]
-            self.k_norm = tensors.get(p + "k_norm.weight")
+            self.q_norm = tensors[p + nm["q_norm"]]
+            self.k_norm = tensors.get(p + nm["k_norm"])
+        if s.distance_bias is not None:
+            slopes = [2.0 ** (-float(s.distance_bias) * (h + 1) / s.n_heads) for h in range(s.n_heads)]
+            self.slopes = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(self.w_o.device)
 
     def weight_bytes(self) -> int:
-        ts = [self.w_qkv, self.w_o, self.q_norm, self.k_norm]
+        ts = [self.w_qkv, self.w_o, self.q_norm, self.k_norm, self.slopes]
         return sum(t.numel() * t.element_size() for t in ts if t is not None)
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed.paged_kv(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
+        s = self.spec
+        if s.value_dim != s.head_dim:
+            return CacheNeed.paged((CachedTensor("k", s.n_kv_heads, s.head_dim), CachedTensor("v", s.n_kv_heads, s.value_dim)),
+                                   s.window)
+        return CacheNeed.paged_kv(s.n_kv_heads, s.head_dim, s.window)
 
     # ---------------------------------------------------------------- one step
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: CacheView) -> torch.Tensor:
         s = self.spec
         n = ctx.n_tokens
         n_kv = s.n_kv_heads if s.own_kv else 0
-        qkv = ctx.scratch("attn.qkv", (n, (s.n_heads + 2 * n_kv) * s.head_dim))
+        qkv = ctx.scratch("attn.qkv", (n, s.n_heads * s.head_dim + n_kv * (s.head_dim + s.value_dim)))
         ops.linear(h, self.w_qkv, qkv)
-        o = self._attend(ctx, qkv, cache)
+        o = self._attend_general(ctx, qkv, cache) if self.general else self._attend(ctx, qkv, cache)
         out = ctx.scratch("attn.out", (n, s.hidden))
-        ops.linear(o.view(n, s.n_heads * s.head_dim), self.w_o, out)
+        ops.linear(o.view(n, s.n_heads * s.value_dim), self.w_o, out)
         return out
+
+    def _attend_general(self, ctx: StepContext, qkv: torch.Tensor, cache: CacheView) -> torch.Tensor:
+        """Queries to float32, keys and values to their pages, then the general kernel: o [N, heads, value_dim]."""
+        s = self.spec
+        n = ctx.n_tokens
+        n_kv = s.n_kv_heads if s.own_kv else 0
+        q = ctx.scratch("attn.q32", (n, s.n_heads, s.head_dim), torch.float32)
+        ops.qkv_split_write(qkv, q, cache.k_pool if n_kv else None, cache.v_pool if n_kv else None,
+                            cache.slots if n_kv else None, s.n_heads, n_kv, s.head_dim, s.value_dim, cache.page_size)
+        o = ctx.scratch("attn.o", (n, s.n_heads, s.value_dim))
+        ops.paged_attention_general(ctx, q, cache.k_pool, cache.v_pool, o, cache.block_table, s.scale, s.window, s.chunk,
+                                    self.slopes)
+        return o
 
     def forward_normed(self, ctx: StepContext, residual: torch.Tensor, norm, cache: CacheView, next_norm=None) -> bool:
         s = self.spec
         n = ctx.n_tokens
-        if n > 16 or not isinstance(norm, RMSNorm) or self.dtype != torch.bfloat16:
+        if n > 16 or not isinstance(norm, RMSNorm) or self.dtype != torch.bfloat16 or self.general:
             return False
         if not (ops.fused_projection_supported(n, self.w_qkv) and ops.fused_projection_supported(n, self.w_o)):
             return False

@@ -87,6 +87,10 @@ class StepContext:
         # the activation dtype, parts of the rows' sums of squares).  Valid while nothing else touches the residual.
         self.prepared_norms: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self.next_norm = None                   # the first norm of the block that runs after the current one, if known
+        # A norm that was already applied to the residual as it stands, by that norm's id: the normalised rows in the
+        # activation dtype.  Valid while nothing else touches the residual.
+        self.normed: Dict[int, torch.Tensor] = {}
+        self.on_layer = None                    # called as on_layer(index in the run order, residual, pending delta) behind every layer call
 
     def scratch(self, tag: str, shape: Sequence[int], dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return self.runner.scratch(tag, tuple(shape), dtype or self.dtype)

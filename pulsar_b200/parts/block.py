@@ -7,7 +7,9 @@ import torch
 
 from ..config.registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
 from ..config.specs import BlockSpec
+from .. import ops
 from .base import Block, CacheView, StepContext, WeightSpec
+from .norm import RMSNorm
 
 
 @BLOCKS.register("prenorm")
@@ -48,3 +50,71 @@ class PreNormBlock(Block):
         ctx.prepared_norms.clear()
         h = self.feed_forward_norm.forward(ctx, residual, delta)
         return self.feed_forward.forward(ctx, h)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """x += post1(mixer(norm1(x))); x += post2(feed_forward(norm2(x))): every sublayer is normed before and behind.  A block
+    without a feed-forward has the first sublayer only.  All four norms are RMS norms.
+
+    The stream is complete when the block returns (nothing is left pending).  One kernel stands between two sublayers:
+    it norms the sublayer's output, adds it to the float32 stream and applies the next sublayer's first norm
+    (``ops.post_norm_add``); where the next block's first norm is known (``ctx.next_norm``) the block's last such kernel
+    applies it and leaves the result in ``ctx.normed`` for whoever comes next."""
+
+    def __init__(self, spec: BlockSpec, dtype: torch.dtype):
+        self.spec = spec
+
+        def norm(norm_spec, part, tag):
+            made = NORMS.get(norm_spec.kind)(norm_spec, spec.sub_prefix(part), dtype, tag)
+            if not isinstance(made, RMSNorm):
+                raise ValueError(f"a sandwich block's norms are RMS norms, '{norm_spec.kind}' is not")
+            return made
+        if spec.mixer_post_norm is None:
+            raise ValueError("a sandwich block needs a norm behind its mixer")
+        self.mixer_norm = norm(spec.mixer_norm, "mixer_norm", "norm.mixer")
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, spec.sub_prefix("mixer"), dtype)
+        self.mixer_post_norm = norm(spec.mixer_post_norm, "mixer_post_norm", "norm.mixer.post")
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        if spec.feed_forward is not None:
+            if spec.feed_forward_norm is None or spec.feed_forward_post_norm is None:
+                raise ValueError("a sandwich block with a feed-forward needs the norms before and behind it")
+            self.feed_forward_norm = norm(spec.feed_forward_norm, "feed_forward_norm", "norm.ffn")
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, spec.sub_prefix("feed_forward"), dtype)
+            self.feed_forward_post_norm = norm(spec.feed_forward_post_norm, "feed_forward_post_norm", "norm.ffn.post")
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.feed_forward_norm,
+                                       self.feed_forward, self.feed_forward_post_norm) if p is not None)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [w for p in self.parts for w in p.weight_specs()]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts:
+            p.load(tensors)
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in self.parts)
+
+    def forward(self, ctx: StepContext, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                cache: CacheView) -> Optional[torch.Tensor]:
+        ctx.prepared_norms.clear()
+        h = ctx.normed.pop(id(self.mixer_norm), None) if delta is None else None
+        ctx.normed.clear()
+        if h is None:
+            h = self.mixer_norm.forward(ctx, residual, delta)
+        out = self.mixer.forward(ctx, h, cache)
+        post = self.mixer_post_norm
+        if self.feed_forward is not None:
+            nxt = self.feed_forward_norm
+            h = ctx.scratch(nxt.tag, residual.shape)
+            ops.post_norm_add(residual, out, post.weight, post.spec.eps, nxt.weight, nxt.spec.eps, h)
+            out = self.feed_forward.forward(ctx, h)
+            post = self.feed_forward_post_norm
+        nxt = ctx.next_norm
+        if isinstance(nxt, RMSNorm) and nxt.spec.size == residual.shape[1]:
+            h = ctx.scratch("norm.ahead", residual.shape)
+            ops.post_norm_add(residual, out, post.weight, post.spec.eps, nxt.weight, nxt.spec.eps, h)
+            ctx.normed[id(nxt)] = h
+        else:
+            ops.post_norm_add(residual, out, post.weight, post.spec.eps)
+        return None

@@ -60,3 +60,45 @@ class SwiGLU(FeedForward):
         out = ctx.scratch("mlp.out", (n, s.hidden))
         ops.linear(act, self.w_down, out)
         return out
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(FeedForward):
+    """g = min(h Wg^T, limit), u = clamp(h Wu^T, -limit, limit); out = (g * sigmoid(alpha * g) * (u + 1)) Wd^T, without bias.
+    Gate and up are one fused product (rows: gate | up); the gating runs in float32 and rounds once.
+    Options (``spec.extra``): ``limit``, ``alpha``; tensor names by role "gate", "up", "down"."""
+
+    def __init__(self, spec: FeedForwardSpec, prefix: str, dtype: torch.dtype):
+        self.limit = float(spec.option("limit", 0.0))
+        self.alpha = float(spec.option("alpha", 1.702))
+        if not (self.limit > 0.0):
+            raise ValueError("clamped_glu: the clamp's limit must be positive")
+        self.spec, self.prefix, self.dtype = spec, prefix, dtype
+        names = dict(spec.option("tensor_names", ()))
+        self.names = {r: names.get(r, d) for r, d in (("gate", "gate_proj.weight"), ("up", "up_proj.weight"),
+                                                      ("down", "down_proj.weight"))}
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        s, p, nm = self.spec, self.prefix, self.names
+        return [WeightSpec(p + nm["gate"], (s.intermediate, s.hidden)),
+                WeightSpec(p + nm["up"], (s.intermediate, s.hidden)),
+                WeightSpec(p + nm["down"], (s.hidden, s.intermediate))]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        p, nm = self.prefix, self.names
+        self.w_gate_up = torch.cat([tensors[p + nm["gate"]], tensors[p + nm["up"]]], dim=0).contiguous()
+        self.w_down = tensors[p + nm["down"]]
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        s, n = self.spec, ctx.n_tokens
+        gate_up = ctx.scratch("mlp.gate_up", (n, 2 * s.intermediate))
+        ops.linear(h, self.w_gate_up, gate_up)
+        act = ctx.scratch("mlp.act", (n, s.intermediate))
+        ops.clamped_glu(gate_up, act, self.limit, self.alpha)
+        out = ctx.scratch("mlp.out", (n, s.hidden))
+        ops.linear(act, self.w_down, out)
+        return out

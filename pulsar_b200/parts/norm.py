@@ -21,10 +21,10 @@ class RMSNorm(Norm):
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.prefix + "weight", (self.spec.size,), role="vector", init="ones_normal")]
+        return [WeightSpec(self.prefix + self.spec.suffix, (self.spec.size,), role="vector", init="ones_normal")]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors[self.prefix + "weight"]
+        self.weight = tensors[self.prefix + self.spec.suffix]
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -27,6 +27,17 @@ def _draw(spec: WeightSpec, std: float, gen: torch.Generator, device) -> torch.T
         return 1.0 + 0.1 * noise
     if spec.init == "normal":
         return std * noise
+    # what a recurrent mixer's small tensors need so that its state neither dies nor explodes
+    if spec.init == "wide":                     # a projection with few inputs
+        return noise / max(1.0, float(spec.shape[-1])) ** 0.5
+    if spec.init == "taps":                     # taps of a short convolution
+        return 0.5 * noise
+    if spec.init == "small":
+        return 0.1 * noise
+    if spec.init == "step_bias":                # softplus of it is a step size around 0.1 to 0.7
+        return -1.0 + 0.7 * noise
+    if spec.init == "decay_log":                # exp of it is a decay rate between 0.5 and 8
+        return torch.log(0.5 + 7.5 * torch.rand(spec.shape, generator=gen, dtype=torch.float32, device=device))
     raise ValueError(f"weight '{spec.name}': unknown init '{spec.init}'")
 
 
