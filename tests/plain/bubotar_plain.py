@@ -67,23 +67,31 @@ def distance_slopes(n_heads: int, dtype) -> torch.Tensor:
     return torch.tensor([2.0 ** (-8.0 * (k + 1) / n_heads) for k in range(n_heads)], dtype=dtype)
 
 
+def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, slopes: Optional[torch.Tensor] = None,
+                    chunk: Optional[int] = None, window: Optional[int] = None, first: int = 0) -> torch.Tensor:
+    """q [Lq, H, D], k [L, H, D], v [L, H, Dv] with one key/value head per query head; the queries sit at positions
+    first .. first + Lq - 1, the keys at 0 .. L - 1.  Causal; optional distance bias, chunk mask and window."""
+    qpos, kpos = first + torch.arange(q.shape[0]), torch.arange(k.shape[0])
+    scores = torch.einsum("ihd,jhd->hij", q, k) * scale
+    if slopes is not None:
+        scores = scores - slopes.to(q.dtype)[:, None, None] * (qpos[:, None] - kpos[None, :]).to(q.dtype)[None]
+    visible = kpos[None, :] <= qpos[:, None]
+    if chunk:
+        visible = visible & ((kpos[None, :] // chunk) == (qpos[:, None] // chunk))
+    if window:
+        visible = visible & (kpos[None, :] > qpos[:, None] - window)
+    return torch.einsum("hij,jhd->ihd", softmax_rows(scores, visible[None]), v)
+
+
 def chunked_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict) -> torch.Tensor:
     """Grouped heads, no rotation; the score loses slope_h * (i - j); a query sees earlier keys of its own chunk."""
     L = h.shape[0]
     H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    pos = torch.arange(L)
     q = (h @ w["q"].T).view(L, H, dim)
     k = (h @ w["k"].T).view(L, G, dim).repeat_interleave(H // G, dim=1)
     v = (h @ w["v"].T).view(L, G, vdim).repeat_interleave(H // G, dim=1)
-    scores = torch.einsum("ihd,jhd->hij", q, k) * m["scale"]
-    distance = (pos[:, None] - pos[None, :]).to(h.dtype)
-    scores = scores - distance_slopes(H, h.dtype)[:, None, None] * distance[None]
-    visible = pos[None, :] <= pos[:, None]
-    size = (m.get("mask") or {}).get("size")
-    if size:
-        visible = visible & ((pos[None, :] // size) == (pos[:, None] // size))
-    p = softmax_rows(scores, visible[None])
-    return torch.einsum("hij,jhd->ihd", p, v).reshape(L, H * vdim) @ w["o"].T
+    out = dense_attention(q, k, v, m["scale"], distance_slopes(H, h.dtype), (m.get("mask") or {}).get("size"))
+    return out.reshape(L, H * vdim) @ w["o"].T
 
 
 def silu(x: torch.Tensor) -> torch.Tensor:
@@ -163,3 +171,11 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
         if residuals is not None:
             residuals.append(x.clone())
     return (rms_norm(x, w["final.norm"], eps) @ w["head"].T) * cfg.get("logit_scale", 1.0)
+
+
+def greedy_generate(cfg: dict, weights: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        out.append(int(torch.argmax(forward(cfg, weights, seq)[-1])))
+        seq.append(out[-1])
+    return out
