@@ -1,0 +1,228 @@
+"""Throughput of another design beside the closest dense model at equal size (``bench.py --design NAME``).
+
+For each size the design's model and a Qwen3 dense model of the same width, depth, heads, feed-forward size and vocabulary
+are built with random weights (bfloat16) and timed through the step function:
+
+  prefill   one step of 2,048 prompt tokens (tokens a second, ms)
+  decode    steps of single tokens of 8 requests whose context ends at 2,048 (tokens a second, ms per step)
+
+and one prefill step and a few decode steps are run once more with every launch bracketed by CUDA events, which gives
+the device time per kernel class.  For the kernels that are the design's own, and for the dense model's like kernels,
+the line states the work the kernel must do (bytes it must move, floating-point operations), the time that work takes
+at the peaks (copy bandwidth; the bf16 tensor peak for contractions) and the fraction of it that was reached.
+"""
+from __future__ import annotations
+
+import json
+import math
+from typing import Dict, List, Tuple
+
+PAGE = 16
+PROMPT = 2048
+BATCH, CONTEXT = 8, 2048
+
+# Sizes that resemble layers of real models.  A group of four layers: latent attention with its own latent, the
+# recurrent mixer (no feed-forward), chunked attention, latent attention on the borrowed latent.
+SIZES = {
+    "2k": dict(width=2048, groups=2, heads=16, kv_heads=4, dim=128, rot=64, rank=512, inner=4096, state=16, dt_rank=128,
+               conv=4, ff=8192, chunk=1024, vocab=32000),
+    "4k": dict(width=4096, groups=2, heads=32, kv_heads=8, dim=128, rot=64, rank=512, inner=8192, state=16, dt_rank=256,
+               conv=4, ff=12288, chunk=1024, vocab=32000),
+}
+
+
+def bubotar_config(z: dict) -> dict:
+    lat = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot"], vdim=z["dim"], kv_rank=z["rank"],
+               scale=1.0 / math.sqrt(z["dim"] + z["rot"]), rot=dict(base=10000.0, dims=z["rot"]))
+    mlp = dict(kind="dense", ff=z["ff"], limit=7.0)
+    layers = []
+    for g in range(z["groups"]):
+        layers += [dict(type="latent_attention", mixer=dict(lat), mlp=dict(mlp)),
+                   dict(type="mamba1", mixer=dict(inner=z["inner"], state=z["state"], dt_rank=z["dt_rank"], conv=z["conv"]), mlp=None),
+                   dict(type="attention", mixer=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"],
+                                                     scale=1.0 / math.sqrt(z["dim"]), mask=dict(size=z["chunk"])), mlp=dict(mlp)),
+                   dict(type="latent_attention", mixer=dict(lat, kv_from=4 * g), mlp=dict(mlp))]
+    return dict(architecture="Bubotar", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), logit_scale=1.0, layers=layers)
+
+
+def dense_config(z: dict) -> dict:
+    n = 4 * z["groups"]
+    return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=z["vocab"], hidden_size=z["width"],
+                intermediate_size=z["ff"], num_hidden_layers=n, num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                head_dim=z["dim"], rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=False,
+                sliding_window=None, max_window_layers=n, hidden_act="silu", attention_bias=False, initializer_range=0.02,
+                eos_token_id=-1)
+
+
+def build(raw: dict):
+    import torch
+    from pulsar_b200.config import config_from_dict
+    from pulsar_b200.engine.engine import Engine
+    from pulsar_b200.models import build_model
+    from pulsar_b200.weights import load_random
+    cfg = config_from_dict(raw)
+    model = build_model(cfg, torch.bfloat16)
+    load_random(model, 0, 0.02, "cuda:0")
+    pages = BATCH * (-(-(CONTEXT + PAGE) // PAGE)) + PROMPT // PAGE + 8
+    engine = Engine.from_model(cfg, model, dict(dtype="bfloat16", device="cuda:0", page_size=PAGE, num_pages=pages,
+                                                max_sessions=BATCH + 1, max_running=BATCH + 1, max_chunk_size=PROMPT, eos_id=-1,
+                                                temperature=0.0))
+    for g in engine.cache.groups:
+        for pool in g.pools.values():
+            pool.normal_(0.0, 1.0)
+    return engine
+
+
+def profiled(engine, bench) -> Tuple[Dict[str, List[float]], Dict[str, List[float]]]:
+    """Device time per kernel class of one prefill step and of four decode steps, launch by launch."""
+    import torch
+    from pulsar_b200 import ops, profiling
+    from pulsar_b200.engine.runner import StepEntry
+    runner, cache = engine.runner, engine.cache
+    saved = (profiling.ENABLED, runner.cuda_graphs)
+    profiling.ENABLED, runner.cuda_graphs = True, False
+    ops._fns.clear()
+    try:
+        gen = torch.Generator().manual_seed(5)
+        vocab = engine.model.spec.vocab_size
+        prompt = torch.randint(0, vocab, (PROMPT,), generator=gen).tolist()
+        out = []
+        for phase in ("prefill", "decode"):
+            for measured in (False, True):           # once unmeasured: buffers reach their size
+                if phase == "prefill":
+                    profiling.reset()
+                    runner.step([StepEntry("p", prompt, [PROMPT - 1])])
+                    runner.finish("p")
+                else:
+                    rids = [("d", i) for i in range(BATCH)]
+                    for rid in rids:
+                        cache.open(rid)
+                        cache.append(rid, CONTEXT - 5)
+                    runner.step([StepEntry(rid, [1], [0]) for rid in rids])
+                    profiling.reset()
+                    for _ in range(4):
+                        runner.step([StepEntry(rid, [1], [0]) for rid in rids])
+                    if measured:
+                        out.append(profiling.totals()[0])
+                    for rid in rids:
+                        runner.finish(rid)
+                    continue
+                if measured:
+                    out.append(profiling.totals()[0])
+        return out[0], out[1]
+    finally:
+        profiling.ENABLED, runner.cuda_graphs = saved
+        ops._fns.clear()
+        profiling.reset()
+
+
+def _pairs(n_new: int, start: int, chunk: int = 0) -> float:
+    """(query, visible key) pairs of n_new tokens that follow `start` cached ones."""
+    total = 0.0
+    for p in (range(start, start + n_new) if n_new < 64 else ()):
+        total += p - (p // chunk * chunk if chunk else 0) + 1
+    if n_new >= 64:                                   # a whole prompt from position 0
+        if chunk:
+            full, rest = divmod(n_new, chunk)
+            total = full * chunk * (chunk + 1) / 2.0 + rest * (rest + 1) / 2.0
+        else:
+            total = n_new * (n_new + 1) / 2.0
+    return total
+
+
+def own_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
+    """Per kernel class of the design: (bytes it must move, flops, what the flops run on) summed over the layers of a step."""
+    n = PROMPT if phase == "prefill" else BATCH
+    seqs = 1 if phase == "prefill" else BATCH
+    ctx = PROMPT if phase == "prefill" else CONTEXT
+    start = 0 if phase == "prefill" else CONTEXT - 1
+    g, H, G, d, rot, rank, w = z["groups"], z["heads"], z["kv_heads"], z["dim"], z["rot"], z["rank"], z["width"]
+    row = rank + rot
+    steps = 1 if phase == "prefill" else 4
+    lat_pairs = seqs * _pairs(n // seqs, start)
+    att_pairs = seqs * _pairs(n // seqs, start, z["chunk"])
+    att_ctx = ctx if phase == "prefill" else (CONTEXT - 1) % z["chunk"] + 1
+    work = {
+        "paged_attention_general": (
+            g * (2 * (seqs * ctx * row * 2 + n * H * (row * 4 + rank * 2)) + seqs * att_ctx * G * 2 * d * 2 + n * H * d * 6),
+            g * (2 * 2.0 * H * (row + rank) * lat_pairs + 2.0 * H * 2 * d * att_pairs), "fp32 FMA"),
+        "heads_linear": (g * 2 * (2 * H * d * rank * 2 + n * H * (d * 2 + rank * 4 + rank * 2 + d * 2 + d * 2)),
+                         g * 2 * 2.0 * n * H * d * rank * 2, "fp32 FMA"),
+        "latent_prepare": (g * (2 * n * H * (rot * 2 + rot * 4) + n * row * 4), 0.0, ""),
+        "qkv_split_write": (g * n * (H + 2 * G) * d * (2 + 4), 0.0, ""),
+        "causal_conv_silu": (g * n * z["inner"] * 4, 0.0, ""),
+        "selective_scan": (g * (n * (z["inner"] * 8 + (z["dt_rank"] + 2 * z["state"]) * 2) + seqs * z["inner"] * z["state"] * 8
+                                + z["inner"] * (z["dt_rank"] * 2 + z["state"] * 4)),
+                           g * n * z["inner"] * (2.0 * z["dt_rank"] + 7.0 * z["state"]), "fp32 FMA"),
+        "post_norm_add": (g * 7 * n * w * (4 + 4 + 2 + 2), 0.0, ""),
+        "clamped_glu": (g * 3 * n * z["ff"] * 6, 0.0, ""),
+    }
+    work["paged_attention_general_tiled"] = work["paged_attention_general"]          # the same job, by the other kernel
+    return {k: (b * steps, f * steps, on) for k, (b, f, on) in work.items()}
+
+
+def like_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
+    """The same for the dense model's kernels that do the like jobs."""
+    n = PROMPT if phase == "prefill" else BATCH
+    layers, H, G, d, w = 4 * z["groups"], z["heads"], z["kv_heads"], z["dim"], z["width"]
+    steps = 1 if phase == "prefill" else 4
+    if phase == "prefill":
+        work = {"paged_attention_prefill_tcgen05": (layers * (PROMPT * (2 * H + 2 * G) * d * 2),
+                                                    layers * 4.0 * H * d * PROMPT * (PROMPT + 1) / 2.0, "bf16 tensor"),
+                "silu_mul": (0.0, 0.0, "")}
+    else:
+        work = {"paged_attention_decode_tc": (layers * BATCH * CONTEXT * 2 * G * d * 2, 0.0, ""),
+                "paged_attention_decode_tc_qkv": (layers * BATCH * CONTEXT * 2 * G * d * 2, 0.0, "")}
+    work["add_rmsnorm"] = ((2 * layers + 1) * n * w * (4 + 4 + 2 + 2), 0.0, "")
+    work["qk_norm_rope_write"] = (layers * n * (H + 2 * G) * d * 4, 0.0, "")
+    return {k: (b * steps, f * steps, on) for k, (b, f, on) in work.items()}
+
+
+def rooflines(kernels: Dict[str, List[float]], work: Dict[str, Tuple[float, float, str]], pk: dict) -> dict:
+    fp32_tflops = 148 * 128 * 2 * 1.965e9 / 1e12            # FMA lanes x 2 x the maximum SM clock: what float32 arithmetic can reach
+    out = {}
+    for name, (n, ms) in sorted(kernels.items(), key=lambda kv: -kv[1][1]):
+        if name not in work or ms <= 0.0:
+            continue
+        nbytes, flops, on = work[name]
+        if nbytes <= 0.0 and flops <= 0.0:
+            continue
+        t_mem = nbytes / (pk["hbm_gbs"] * 1e9)
+        peak = pk["bf16_tflops"] if on == "bf16 tensor" else fp32_tflops
+        t_math = flops / (peak * 1e12) if flops else 0.0
+        out[name] = {"launches": int(n), "ms": round(ms, 4), "gbytes": round(nbytes / 1e9, 4), "gflop": round(flops / 1e9, 2),
+                     "bound": "memory" if t_mem >= t_math else on, "frac_of_roofline": round(max(t_mem, t_math) * 1e3 / ms, 4)}
+    return out
+
+
+def run(args, bench) -> dict:
+    """``bench``: the bench module (its timing functions, peaks and clock sampler are used as they are)."""
+    import torch
+    pk = bench.peaks()
+    sizes = [s for s in (args.sizes.split(",") if args.sizes else SIZES) if s]
+    line = {"design": args.design, "dtype": "bf16", "data": "synthetic: random weights, random token ids, random cache contents for decode",
+            "prompt_tokens": PROMPT, "decode": {"batch": BATCH, "context": CONTEXT}, "peaks": pk, "sizes": {}}
+    for size in sizes:
+        z = SIZES[size]
+        entry = {"shape": z}
+        for who, raw in (("design", bubotar_config(z)), ("dense", dense_config(z))):
+            engine = build(raw)
+            p_seconds = bench.time_prefill(engine, PROMPT)
+            d_seconds, _, _ = bench.time_decode(engine, BATCH, CONTEXT, args.steps, max(3, args.warmup))
+            prefill_k, decode_k = profiled(engine, bench)
+            work = own_work if who == "design" else like_work
+            entry[who] = {
+                "model": engine.model.spec.architecture, "weights_gb": round(engine.model.weight_bytes(0) / 1e9, 3),
+                "prefill_tokens_per_s": round(PROMPT / p_seconds, 1), "prefill_ms": round(p_seconds * 1e3, 3),
+                "decode_tokens_per_s": round(BATCH * args.steps / d_seconds, 1), "decode_ms_per_step": round(d_seconds / args.steps * 1e3, 4),
+                "decode_hbm_frac": round(bench.decode_bytes(engine, BATCH, CONTEXT - args.steps / 2.0) / (d_seconds / args.steps) / 1e9
+                                         / pk["hbm_gbs"], 4),
+                "prefill_kernels": rooflines(prefill_k, work(z, "prefill"), pk),
+                "decode_kernels": rooflines(decode_k, work(z, "decode"), pk),
+                "prefill_ms_by_class": {k: round(v[1], 3) for k, v in sorted(prefill_k.items(), key=lambda kv: -kv[1][1])[:12]},
+                "decode_ms_by_class_4_steps": {k: round(v[1], 3) for k, v in sorted(decode_k.items(), key=lambda kv: -kv[1][1])[:12]},
+            }
+            del engine
+            torch.cuda.empty_cache()
+        line["sizes"][size] = entry
+    return line

@@ -185,6 +185,304 @@ int dispatch_general(const float* q, const void* k_pool, const void* v_pool, voi
 #undef PB_GENERAL
 }
 
+// ---------------------------------------------------------------- the tiled form
+// The same arithmetic with the keys and values of a tile staged in shared memory and shared by 16 query rows: the rows of
+// a block are consecutive (token, head) pairs of one sequence and one key/value head (index = token * group + head in
+// group), so a step of single tokens shares a tile among the heads of a group and a prompt portion among tokens as well.
+// Warp w owns rows 4w .. 4w+3; its lane l scores key l of the tile against the four rows (the key's elements come from
+// shared memory 16 bytes at a time, the queries by broadcast), the warp reduces maxima and sums over its lanes, and lane l
+// then owns value columns l, l + 32, ... of the four rows' outputs.  Tiles of 32 keys are aligned to absolute key
+// indices and taken in ascending order; a tile in which a row sees nothing leaves that row's state untouched, so a row's
+// result depends on its own position alone.  With splits (grid z) each block takes a contiguous share of the tiles and
+// writes (maximum, sum, unnormalised output) per row to a float32 workspace that general_combine_kernel merges in split
+// order.  Needs key and value rows that are multiples of 16 bytes; other sizes take the kernel above.
+constexpr int kRows = 16;
+constexpr int kTile = 32;
+
+struct TiledShape {
+    GeneralShape g;
+    int n_seqs, n_splits, k_row, v_row;      // rows of the staged tiles in elements (k_row padded; v_row = k_row when the value is part of the key row)
+    int v_in_k;
+};
+
+template <typename T> __device__ __forceinline__ void zero16(T* p) { *reinterpret_cast<uint4*>(p) = make_uint4(0, 0, 0, 0); }
+
+template <typename T, int ACC>
+__global__ void __launch_bounds__(128)
+general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool, T* __restrict__ out,
+                     float* __restrict__ partial, const int* __restrict__ block_table, const int* __restrict__ cu_q,
+                     const int* __restrict__ kv_len, const float* __restrict__ slopes, const TiledShape ts,
+                     const PoolBounds bounds) {
+    constexpr int V = Vec<T>::n;
+    const GeneralShape& sh = ts.g;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int Dk = sh.Dk, Dv = sh.Dv, GH = sh.Hq / sh.Hkv;
+    float* q_s = reinterpret_cast<float*>(smem_raw);                         // [kRows][Dk], times scale
+    float* p_s = q_s + kRows * Dk;                                            // [kRows][kTile]
+    T* k_s = reinterpret_cast<T*>(p_s + kRows * kTile);                       // [kTile][k_row]
+    T* v_s = ts.v_in_k ? k_s : k_s + (size_t)kTile * ts.k_row;                // [kTile][v_row]
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = blockIdx.y, split = blockIdx.z;
+    int tile = blockIdx.x, s = 0, q0 = 0, q_len = 0;
+    for (; s < ts.n_seqs; ++s) {
+        q0 = cu_q[s];
+        q_len = cu_q[s + 1] - q0;
+        const int nt = (q_len * GH + kRows - 1) / kRows;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (s >= ts.n_seqs) return;
+    const int ctx0 = kv_len[s] - q_len;
+    const int idx0 = tile * kRows;
+    const int n_rows = min(kRows, q_len * GH - idx0);
+    const int* table = block_table + (size_t)s * sh.table_stride;
+
+    // the block's span of keys: from the lowest key any row sees to the highest
+    int lo_blk = 0x7fffffff, hi_blk = 0;
+    for (int r = 0; r < n_rows; ++r) {
+        const int p = ctx0 + (idx0 + r) / GH;
+        int lo = 0;
+        if (sh.window > 0 && p - sh.window + 1 > lo) lo = p - sh.window + 1;
+        if (sh.chunk > 0 && (p / sh.chunk) * sh.chunk > lo) lo = (p / sh.chunk) * sh.chunk;
+        lo_blk = min(lo_blk, lo);
+        hi_blk = max(hi_blk, p);
+    }
+    const int kt0 = lo_blk / kTile, n_tiles = hi_blk / kTile - kt0 + 1;
+    const int per = (n_tiles + ts.n_splits - 1) / ts.n_splits;
+    const int t_begin = kt0 + split * per, t_end = min(kt0 + n_tiles, t_begin + per);
+
+    // this thread's four rows
+    int pos[4], lo_r[4], tok[4], head[4];
+    float slope[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int row = warp * 4 + r;
+        const bool on = row < n_rows;
+        const int idx = idx0 + (on ? row : 0);
+        tok[r] = q0 + idx / GH;
+        head[r] = g * GH + idx % GH;
+        pos[r] = on ? ctx0 + idx / GH : -1;                  // -1: sees no key
+        int lo = 0;
+        if (sh.window > 0 && pos[r] - sh.window + 1 > lo) lo = pos[r] - sh.window + 1;
+        if (sh.chunk > 0 && pos[r] >= 0 && (pos[r] / sh.chunk) * sh.chunk > lo) lo = (pos[r] / sh.chunk) * sh.chunk;
+        lo_r[r] = lo;
+        slope[r] = slopes ? slopes[head[r]] : 0.0f;
+    }
+    for (int i = threadIdx.x; i < kRows * Dk; i += blockDim.x) {
+        const int row = i / Dk, d = i % Dk;
+        float v = 0.0f;
+        if (row < n_rows) {
+            const int idx = idx0 + row;
+            v = q[((size_t)(q0 + idx / GH) * sh.Hq + g * GH + idx % GH) * Dk + d] * sh.scale;
+        }
+        q_s[i] = v;
+    }
+
+    float m_run[4], l_run[4], acc[4][ACC];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        m_run[r] = -INFINITY;
+        l_run[r] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < ACC; ++i) acc[r][i] = 0.0f;
+    }
+
+    const int k_chunks = Dk / V, v_chunks = Dv / V;
+    for (int kt = t_begin; kt < t_end; ++kt) {
+        const int j0 = kt * kTile;
+        __syncthreads();                                   // the tile before is done with (and q_s is written)
+        for (int c = threadIdx.x; c < kTile * k_chunks; c += blockDim.x) {
+            const int key = c / k_chunks, part = c % k_chunks;
+            const int j = j0 + key;
+            T* dst = k_s + (size_t)key * ts.k_row + part * V;
+            if (j < lo_blk || j > hi_blk) { zero16(dst); continue; }
+            int page = table[j / sh.page_size];
+            if (!page_ok(page, bounds)) page = 0;
+            const T* src = k_pool + (((size_t)page * sh.Hkv + g) * sh.page_size + j % sh.page_size) * sh.k_stride + part * V;
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+        }
+        if (!ts.v_in_k) {
+            for (int c = threadIdx.x; c < kTile * v_chunks; c += blockDim.x) {
+                const int key = c / v_chunks, part = c % v_chunks;
+                const int j = j0 + key;
+                T* dst = v_s + (size_t)key * ts.v_row + part * V;
+                if (j < lo_blk || j > hi_blk) { zero16(dst); continue; }
+                int page = table[j / sh.page_size];
+                if (!page_ok(page, bounds)) page = 0;
+                const T* src = v_pool + (((size_t)page * sh.Hkv + g) * sh.page_size + j % sh.page_size) * sh.v_stride + part * V;
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+            }
+        }
+        __syncthreads();
+
+        // scores of key `lane` against the warp's four rows
+        float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const T* kr = k_s + (size_t)lane * ts.k_row;
+        const float* qr = q_s + (size_t)(warp * 4) * Dk;
+        for (int d = 0; d < Dk; d += V) {
+            float kf[V];
+            load16(kr + d, kf);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+#pragma unroll
+                for (int e = 0; e < V; e += 4) {
+                    const float4 qv = *reinterpret_cast<const float4*>(qr + r * Dk + d + e);
+                    sc[r] = fmaf(qv.x, kf[e], sc[r]);
+                    sc[r] = fmaf(qv.y, kf[e + 1], sc[r]);
+                    sc[r] = fmaf(qv.z, kf[e + 2], sc[r]);
+                    sc[r] = fmaf(qv.w, kf[e + 3], sc[r]);
+                }
+            }
+        }
+        const int j = j0 + lane;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const bool vis = j >= lo_r[r] && j <= pos[r];
+            const float v = vis ? sc[r] - slope[r] * (float)(pos[r] - j) : -INFINITY;
+            const float m_new = fmaxf(m_run[r], warp_max(v));
+            float pv = 0.0f, corr = 1.0f;
+            if (m_new != -INFINITY) {                       // uniform over the warp
+                pv = vis ? expf(v - m_new) : 0.0f;
+                corr = expf(m_run[r] - m_new);              // 0 while the row had seen nothing
+            }
+            l_run[r] = l_run[r] * corr + warp_sum(pv);
+            m_run[r] = m_new;
+            if (corr != 1.0f) {
+#pragma unroll
+                for (int i = 0; i < ACC; ++i) acc[r][i] *= corr;
+            }
+            p_s[(warp * 4 + r) * kTile + lane] = pv;
+        }
+        __syncwarp();
+        // outputs: lane owns value columns lane + 32 i of the four rows
+        const float* pr = p_s + (warp * 4) * kTile;
+        for (int kk = 0; kk < kTile; kk += 4) {
+            float4 pw[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) pw[r] = *reinterpret_cast<const float4*>(pr + r * kTile + kk);
+#pragma unroll
+            for (int i = 0; i < ACC; ++i) {
+                const int c = lane + 32 * i;
+                if (c < Dv) {
+                    const float v0 = to_float(v_s[(size_t)(kk + 0) * ts.v_row + c]), v1 = to_float(v_s[(size_t)(kk + 1) * ts.v_row + c]);
+                    const float v2 = to_float(v_s[(size_t)(kk + 2) * ts.v_row + c]), v3 = to_float(v_s[(size_t)(kk + 3) * ts.v_row + c]);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        acc[r][i] = fmaf(pw[r].x, v0, acc[r][i]);
+                        acc[r][i] = fmaf(pw[r].y, v1, acc[r][i]);
+                        acc[r][i] = fmaf(pw[r].z, v2, acc[r][i]);
+                        acc[r][i] = fmaf(pw[r].w, v3, acc[r][i]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        if (warp * 4 + r >= n_rows) continue;
+        const size_t row = (size_t)tok[r] * sh.Hq + head[r];
+        if (ts.n_splits == 1) {
+            T* ov = out + row * Dv;
+            const float inv = 1.0f / l_run[r];
+#pragma unroll
+            for (int i = 0; i < ACC; ++i) {
+                const int c = lane + 32 * i;
+                if (c < Dv) ov[c] = from_float<T>(acc[r][i] * inv);
+            }
+        } else {
+            float* pp = partial + (row * ts.n_splits + split) * (Dv + 2);
+            if (lane == 0) { pp[0] = m_run[r]; pp[1] = l_run[r]; }
+#pragma unroll
+            for (int i = 0; i < ACC; ++i) {
+                const int c = lane + 32 * i;
+                if (c < Dv) pp[2 + c] = acc[r][i];
+            }
+        }
+    }
+}
+
+// out[row] = sum over the splits, in their order, of their partial outputs weighted by exp(m_split - m_all), over the
+// weighted sum of their sums.  One block per (token, head).
+template <typename T>
+__global__ void general_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int n_splits, int Dv) {
+    const size_t row = blockIdx.x;
+    const float* pp = partial + row * n_splits * (Dv + 2);
+    float m_all = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) m_all = fmaxf(m_all, pp[(size_t)z * (Dv + 2)]);
+    float l_all = 0.0f;
+    for (int z = 0; z < n_splits; ++z) {
+        const float m = pp[(size_t)z * (Dv + 2)];
+        if (m != -INFINITY) l_all += pp[(size_t)z * (Dv + 2) + 1] * expf(m - m_all);
+    }
+    for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
+        float o = 0.0f;
+        for (int z = 0; z < n_splits; ++z) {
+            const float m = pp[(size_t)z * (Dv + 2)];
+            if (m != -INFINITY) o += pp[(size_t)z * (Dv + 2) + 2 + c] * expf(m - m_all);
+        }
+        out[row * Dv + c] = from_float<T>(o / l_all);
+    }
+}
+
+template <typename T>
+size_t tiled_smem(const TiledShape& ts) {
+    return sizeof(float) * (kRows * ts.g.Dk + kRows * kTile) + sizeof(T) * kTile * ((size_t)ts.k_row + (ts.v_in_k ? 0 : ts.v_row));
+}
+
+template <typename T, int ACC>
+int launch_tiled(const float* q, const void* k_pool, const void* v_pool, void* out, float* partial, const int* block_table,
+                 const int* cu_q, const int* kv_len, const float* slopes, int n_tokens, int row_tiles, const TiledShape& ts,
+                 cudaStream_t stream) {
+    const size_t smem = tiled_smem<T>(ts);
+    static size_t allowed = 48 * 1024;                     // per instantiation
+    if (smem > allowed) {
+        const cudaError_t e = cudaFuncSetAttribute(general_tiled_kernel<T, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        allowed = smem;
+    }
+    dim3 grid(row_tiles, ts.g.Hkv, ts.n_splits);
+    general_tiled_kernel<T, ACC><<<grid, 128, smem, stream>>>(q, (const T*)k_pool, (const T*)v_pool, (T*)out, partial, block_table,
+                                                              cu_q, kv_len, slopes, ts, pb::pool_bounds_now());
+    int status = launch_status();
+    if (status == 0 && ts.n_splits > 1) {
+        int b = 32;
+        while (b < ts.g.Dv && b < 256) b <<= 1;
+        general_combine_kernel<T><<<n_tokens * ts.g.Hq, b, 0, stream>>>(partial, (T*)out, ts.n_splits, ts.g.Dv);
+        status = launch_status();
+    }
+    return status;
+}
+
+template <typename T>
+bool tiled_shape(TiledShape& ts, const void* k_pool, const void* v_pool) {
+    const GeneralShape& sh = ts.g;
+    const size_t e = sizeof(T);
+    if ((sh.Dk * e) % 16 || (sh.Dv * e) % 16 || (sh.k_stride * e) % 16 || (sh.v_stride * e) % 16) return false;
+    if (((uintptr_t)k_pool | (uintptr_t)v_pool) % 16) return false;
+    ts.v_in_k = (k_pool == v_pool && sh.k_stride == sh.v_stride && sh.Dv <= sh.Dk) ? 1 : 0;
+    const int unit = 16 / (int)e;                           // elements in 16 bytes
+    int k_units = sh.Dk / unit;
+    if (k_units % 2 == 0) ++k_units;                        // rows an odd number of 16-byte units apart: lanes on different rows do not collide
+    ts.k_row = k_units * unit;
+    ts.v_row = ts.v_in_k ? ts.k_row : sh.Dv;
+    return tiled_smem<T>(ts) <= 200 * 1024;
+}
+
+template <typename T>
+int dispatch_tiled(const float* q, const void* k_pool, const void* v_pool, void* out, float* partial, const int* block_table,
+                   const int* cu_q, const int* kv_len, const float* slopes, int n_tokens, int row_tiles, const TiledShape& ts,
+                   cudaStream_t stream) {
+#define PB_TILED(A) return launch_tiled<T, A>(q, k_pool, v_pool, out, partial, block_table, cu_q, kv_len, slopes, n_tokens, row_tiles, ts, stream)
+    if (ts.g.Dv <= 64) PB_TILED(2);
+    if (ts.g.Dv <= 128) PB_TILED(4);
+    if (ts.g.Dv <= 256) PB_TILED(8);
+    PB_TILED(16);
+#undef PB_TILED
+}
+
 // One warp per (token, head) of the fused projection row [q: Hq*Dk | k: Hkv*Dk | v: Hkv*Dv]:
 // queries to float32 [N, Hq, Dk], keys and values into the pages of the token's slot.
 template <typename T>
@@ -248,4 +546,40 @@ PB_EXPORT int pb_qkv_split_write(int dtype, const void* qkv, float* q_out, void*
                                                                         pb::pool_bounds_now());
     else return PB_ERR_BAD_DTYPE;
     return launch_status();
+}
+
+// 1 when the tiled form takes these sizes (rows that are multiples of 16 bytes, value rows up to 512 wide), else 0.
+PB_EXPORT int pb_attention_general_tiled_supported(int dtype, const void* k_pool, const void* v_pool, int Hq, int Hkv, int Dk, int Dv,
+                                                   int k_stride, int v_stride) {
+    if (Dk <= 0 || Dv <= 0 || Dv > 512 || Hkv <= 0 || Hq <= 0 || Hq % Hkv || k_stride < Dk || v_stride < Dv) return 0;
+    TiledShape ts{};
+    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, 1, 0, 0, 0, 0, 1.0f};
+    if (dtype == PB_F32) return tiled_shape<float>(ts, k_pool, v_pool) ? 1 : 0;
+    if (dtype == PB_BF16) return tiled_shape<__nv_bfloat16>(ts, k_pool, v_pool) ? 1 : 0;
+    return 0;
+}
+
+// The tiled form of pb_paged_attention_general.  row_tiles: the sum over the sequences of ceil(new tokens * (Hq / Hkv) / 16).
+// n_splits > 1 needs `partial`: float32, n_tokens * Hq * n_splits * (Dv + 2) elements.
+PB_EXPORT int pb_paged_attention_general_tiled(int dtype, const float* q, const void* k_pool, const void* v_pool, void* out,
+                                               float* partial, const int* block_table, int table_stride, const int* cu_q,
+                                               const int* kv_len, const float* slopes, int n_tokens, int n_seqs, int row_tiles,
+                                               int n_splits, int Hq, int Hkv, int Dk, int Dv, int k_stride, int v_stride,
+                                               int page_size, float scale, int window, int chunk, cudaStream_t stream) {
+    if (n_tokens <= 0 || row_tiles <= 0) return 0;
+    if (!pb_attention_general_tiled_supported(dtype, k_pool, v_pool, Hq, Hkv, Dk, Dv, k_stride, v_stride)) return PB_ERR_BAD_SIZE;
+    if (page_size <= 0 || window < 0 || chunk < 0 || n_splits < 1 || n_splits > 65535 || (n_splits > 1 && partial == nullptr))
+        return PB_ERR_BAD_SIZE;
+    if (Hkv > 65535) return PB_ERR_TOO_LARGE;
+    TiledShape ts{};
+    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale};
+    ts.n_seqs = n_seqs;
+    ts.n_splits = n_splits;
+    if (dtype == PB_F32) {
+        tiled_shape<float>(ts, k_pool, v_pool);
+        return dispatch_tiled<float>(q, k_pool, v_pool, out, partial, block_table, cu_q, kv_len, slopes, n_tokens, row_tiles, ts, stream);
+    }
+    tiled_shape<__nv_bfloat16>(ts, k_pool, v_pool);
+    return dispatch_tiled<__nv_bfloat16>(q, k_pool, v_pool, out, partial, block_table, cu_q, kv_len, slopes, n_tokens, row_tiles, ts,
+                                         stream);
 }

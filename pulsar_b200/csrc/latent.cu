@@ -1,11 +1,12 @@
 // Helpers of attention over a compressed latent (one cached row per token: [latent | rotated key part]).
 //
-//   heads_linear     out[n, h, :] = W[h] a[n, h, :] for every head h: the per-head products that
+//   heads_linear     out[n, h, :] = W[h]^T a[n, h, :] (W[h] stored [K, M]) for every head h: the per-head products that
 //                    stand in for expanding the latent into keys and values.  With the key
 //                    expansion W_uk the query side takes q_abs[h] = W_uk[h]^T q_plain[h]
 //                    (so that q_plain . (W_uk[h] c) = q_abs[h] . c), with the value expansion W_uv
-//                    the output side takes W_uv[h] (sum_j p_j c_j).  float32 accumulation in
-//                    ascending k, one thread per output, the tokens of a tile share the weights.
+//                    the output side takes W_uv[h] (sum_j p_j c_j).  float32 accumulation.  A few tokens: a
+//                    block takes 8 tokens x 32 outputs, four slices of K in ascending k each, added in slice
+//                    order (enough blocks to fill the GPU).  Many tokens: 8 tokens x 128 outputs, K whole.
 //                    Optionally multiplies by sigmoid(gate[n, h, :]) (an output gate) in float32.
 //   latent_prepare   per token: RMS norm of the latent part of the down projection (float32),
 //                    rotation of the shared key part at the token's position, both written to
@@ -21,37 +22,104 @@ using namespace pb;
 
 constexpr int kTok = 8;
 
+// Many tokens: one thread per output over the whole of K, 128 outputs a block.
+template <typename T, typename TO>
+__global__ void __launch_bounds__(128)
+heads_linear_wide_kernel(const T* __restrict__ a, long a_tok, int a_head, const T* __restrict__ w, TO* __restrict__ out, long o_tok,
+                         int o_head, const T* __restrict__ gate, long g_tok, int N, int M, int K) {
+    extern __shared__ __align__(16) float smem[];  // [kTok][KP], KP = K rounded up to a multiple of 4 (zeros behind K)
+    float* a_s = smem;
+    const int KP = (K + 3) & ~3;
+    const int n0 = blockIdx.x * kTok, h = blockIdx.y;
+    const int nt = min(kTok, N - n0);
+    for (int i = threadIdx.x; i < kTok * KP; i += blockDim.x) {
+        const int tt = i / KP, k = i % KP;
+        a_s[i] = (tt < nt && k < K) ? to_float(a[(size_t)(n0 + tt) * a_tok + (size_t)h * a_head + k]) : 0.0f;
+    }
+    __syncthreads();
+    const int m = blockIdx.z * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    const T* wh = w + (size_t)h * K * M + m;
+    float acc[kTok];
+#pragma unroll
+    for (int tt = 0; tt < kTok; ++tt) acc[tt] = 0.0f;
+    for (int k = 0; k < KP; k += 4) {
+        float wv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wv[e] = (k + e < K) ? to_float(wh[(size_t)(k + e) * M]) : 0.0f;
+#pragma unroll
+        for (int tt = 0; tt < kTok; ++tt) {
+            const float4 av = *reinterpret_cast<const float4*>(a_s + tt * KP + k);
+            acc[tt] = fmaf(av.x, wv[0], acc[tt]);
+            acc[tt] = fmaf(av.y, wv[1], acc[tt]);
+            acc[tt] = fmaf(av.z, wv[2], acc[tt]);
+            acc[tt] = fmaf(av.w, wv[3], acc[tt]);
+        }
+    }
+    for (int tt = 0; tt < nt; ++tt) {
+        float v = acc[tt];
+        if (gate) {
+            const float gv = to_float(gate[(size_t)(n0 + tt) * g_tok + (size_t)h * M + m]);
+            v *= 1.0f / (1.0f + expf(-gv));
+        }
+        out[(size_t)(n0 + tt) * o_tok + (size_t)h * o_head + m] = from_float<TO>(v);
+    }
+}
+
+constexpr int kSlices = 4;      // a block's 128 threads: 32 outputs x 4 slices of K
+
 template <typename T, typename TO>
 __global__ void __launch_bounds__(128)
 heads_linear_kernel(const T* __restrict__ a, long a_tok, int a_head, const T* __restrict__ w, TO* __restrict__ out, long o_tok,
                     int o_head, const T* __restrict__ gate, long g_tok, int N, int M, int K) {
-    extern __shared__ float a_s[];                 // [kTok][K]
+    extern __shared__ __align__(16) float smem[];
+    const int KS = (((K + kSlices - 1) / kSlices) + 3) & ~3;      // k's per slice, a multiple of 4
+    const int KP = KS * kSlices;
+    float* a_s = smem;                             // [kTok][KP], zeros behind K
+    float* r_s = a_s + kTok * KP;                  // [kSlices][kTok][32] partial sums
     const int n0 = blockIdx.x * kTok, h = blockIdx.y;
     const int nt = min(kTok, N - n0);
-    for (int i = threadIdx.x; i < kTok * K; i += blockDim.x) {
-        const int tt = i / K, k = i % K;
-        a_s[i] = tt < nt ? to_float(a[(size_t)(n0 + tt) * a_tok + (size_t)h * a_head + k]) : 0.0f;
+    for (int i = threadIdx.x; i < kTok * KP; i += blockDim.x) {
+        const int tt = i / KP, k = i % KP;
+        a_s[i] = (tt < nt && k < K) ? to_float(a[(size_t)(n0 + tt) * a_tok + (size_t)h * a_head + k]) : 0.0f;
     }
     __syncthreads();
-    const T* wh = w + (size_t)h * M * K;
-    for (int m = threadIdx.x; m < M; m += blockDim.x) {
-        const T* wr = wh + (size_t)m * K;
-        float acc[kTok];
+    const int mx = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int m = blockIdx.z * 32 + mx;
+    const bool live = m < M;
+    const T* wh = w + (size_t)h * K * M + (live ? m : 0);       // [K, M]: neighbouring threads read neighbouring weights
+    float acc[kTok];
 #pragma unroll
-        for (int tt = 0; tt < kTok; ++tt) acc[tt] = 0.0f;
-        for (int k = 0; k < K; ++k) {
-            const float wv = to_float(wr[k]);
+    for (int tt = 0; tt < kTok; ++tt) acc[tt] = 0.0f;
+    const int k0 = slice * KS;
+    for (int k = k0; k < k0 + KS; k += 4) {
+        float wv[4];
 #pragma unroll
-            for (int tt = 0; tt < kTok; ++tt) acc[tt] = fmaf(a_s[tt * K + k], wv, acc[tt]);
+        for (int e = 0; e < 4; ++e) wv[e] = (live && k + e < K) ? to_float(wh[(size_t)(k + e) * M]) : 0.0f;
+#pragma unroll
+        for (int tt = 0; tt < kTok; ++tt) {
+            const float4 av = *reinterpret_cast<const float4*>(a_s + tt * KP + k);
+            acc[tt] = fmaf(av.x, wv[0], acc[tt]);
+            acc[tt] = fmaf(av.y, wv[1], acc[tt]);
+            acc[tt] = fmaf(av.z, wv[2], acc[tt]);
+            acc[tt] = fmaf(av.w, wv[3], acc[tt]);
         }
-        for (int tt = 0; tt < nt; ++tt) {
-            float v = acc[tt];
-            if (gate) {
-                const float gv = to_float(gate[(size_t)(n0 + tt) * g_tok + (size_t)h * M + m]);
-                v *= 1.0f / (1.0f + expf(-gv));
-            }
-            out[(size_t)(n0 + tt) * o_tok + (size_t)h * o_head + m] = from_float<TO>(v);
+    }
+#pragma unroll
+    for (int tt = 0; tt < kTok; ++tt) r_s[(slice * kTok + tt) * 32 + mx] = acc[tt];
+    __syncthreads();
+    // the slices are added in their order by one thread per (token, output)
+    for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
+        const int tt = i >> 5, x = i & 31, mm = blockIdx.z * 32 + x;
+        if (mm >= M) continue;
+        float v = 0.0f;
+#pragma unroll
+        for (int sl = 0; sl < kSlices; ++sl) v += r_s[(sl * kTok + tt) * 32 + x];
+        if (gate) {
+            const float gv = to_float(gate[(size_t)(n0 + tt) * g_tok + (size_t)h * M + mm]);
+            v *= 1.0f / (1.0f + expf(-gv));
         }
+        out[(size_t)(n0 + tt) * o_tok + (size_t)h * o_head + mm] = from_float<TO>(v);
     }
 }
 
@@ -104,21 +172,28 @@ latent_prepare_kernel(const T* __restrict__ q, long q_tok, const T* __restrict__
 template <typename T, typename TO>
 int launch_heads(const void* a, long a_tok, int a_head, const void* w, void* out, long o_tok, int o_head, const void* gate,
                  long g_tok, int N, int H, int M, int K, cudaStream_t stream) {
-    dim3 grid((N + kTok - 1) / kTok, H);
-    heads_linear_kernel<T, TO><<<grid, 128, sizeof(float) * kTok * K, stream>>>((const T*)a, a_tok, a_head, (const T*)w, (TO*)out,
+    if (N > 2 * kTok) {         // enough token tiles to fill the GPU without cutting K
+        dim3 wide((N + kTok - 1) / kTok, H, (M + 127) / 128);
+        heads_linear_wide_kernel<T, TO><<<wide, 128, sizeof(float) * kTok * ((K + 3) & ~3), stream>>>(
+            (const T*)a, a_tok, a_head, (const T*)w, (TO*)out, o_tok, o_head, (const T*)gate, g_tok, N, M, K);
+        return launch_status();
+    }
+    const int ks = (((K + kSlices - 1) / kSlices) + 3) & ~3;
+    dim3 grid((N + kTok - 1) / kTok, H, (M + 31) / 32);
+    heads_linear_kernel<T, TO><<<grid, 128, sizeof(float) * kTok * (ks * kSlices + kSlices * 32), stream>>>((const T*)a, a_tok, a_head, (const T*)w, (TO*)out,
                                                                                  o_tok, o_head, (const T*)gate, g_tok, N, M, K);
     return launch_status();
 }
 
 }  // namespace
 
-// out[n, h, m] = sum_k a[n, h, k] * w[h, m, k]  (* sigmoid(gate[n, h * M + m]) where a gate is given).
-// a: element (n, h, k) at n * a_tok + h * a_head + k; out likewise with o_tok, o_head; w contiguous [H, M, K].
+// out[n, h, m] = sum_k a[n, h, k] * w[h, k, m]  (* sigmoid(gate[n, h * M + m]) where a gate is given).
+// a: element (n, h, k) at n * a_tok + h * a_head + k; out likewise with o_tok, o_head; w contiguous [H, K, M].
 // dtype: of a, w and gate; out_dtype: of out (float32, or the same as dtype).
 PB_EXPORT int pb_heads_linear(int dtype, int out_dtype, const void* a, long a_tok, int a_head, const void* w, void* out, long o_tok,
                               int o_head, const void* gate, long g_tok, int N, int H, int M, int K, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (H <= 0 || M <= 0 || K <= 0 || K > 1024) return PB_ERR_BAD_SIZE;
+    if (H <= 0 || M <= 0 || K <= 0 || K > 1024 || (M + 31) / 32 > 65535) return PB_ERR_BAD_SIZE;
     if (H > 65535) return PB_ERR_TOO_LARGE;
     if (dtype == PB_F32 && out_dtype == PB_F32)
         return launch_heads<float, float>(a, a_tok, a_head, w, out, o_tok, o_head, gate, g_tok, N, H, M, K, stream);

@@ -84,6 +84,8 @@ _SIGNATURES = {
     "pb_sample_workspace": [_I],
     "pb_argmax": [_P, _I, _I, _P, _P, _P],
     "pb_paged_attention_general": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "pb_attention_general_tiled_supported": [_I, _P, _P, _I, _I, _I, _I, _I, _I],
+    "pb_paged_attention_general_tiled": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_qkv_split_write": [_I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "pb_heads_linear": [_I, _I, _P, _L, _I, _P, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
     "pb_latent_prepare": [_I, _P, _L, _P, _L, _P, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -99,7 +101,7 @@ _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk
               "paged_attention_decode_tc_qkv",
               "paged_attention_prefill_tc", "paged_attention_prefill_tcgen05", "gemm_skinny", "gemm_skinny_accumulate",
               "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update",
-              "paged_attention_general", "qkv_split_write", "heads_linear", "latent_prepare", "causal_conv_silu",
+              "paged_attention_general", "paged_attention_general_tiled", "qkv_split_write", "heads_linear", "latent_prepare", "causal_conv_silu",
               "selective_scan", "post_norm_add", "clamped_glu"}
 
 
@@ -875,14 +877,31 @@ def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, wind
 
 
 # ---------------------------------------------------------------- attention in its general form, latent attention
+# The general attention has two kernels: the tiled one (keys and values of a tile staged in shared memory and shared by 16
+# query rows; splits of the keys where the rows alone do not fill the GPU) for rows that are multiples of 16 bytes, and the
+# plain one (a block per token and head) for every other size.  PULSAR_GENERAL_TILED=0 leaves the tiled one out.
+GENERAL_TILED = os.environ.get("PULSAR_GENERAL_TILED", "1") != "0"
+GENERAL_ROWS = 16
+
+
+def general_splits(blocks: int, table_tokens: int) -> int:
+    """Splits of the keys for the tiled general attention: as many as bring the grid to two blocks per SM, at most 32 and
+    at most one per 64 tokens that the block table can name.  A function of the step's shape alone (not of the lengths),
+    so that a captured step stays valid while its sequences grow."""
+    if blocks >= _DECODE_SLOTS:
+        return 1
+    return max(1, min(32, _DECODE_SLOTS // max(1, blocks), table_tokens // 64))
+
+
 def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                             block_table: torch.Tensor, scale: float, window: Optional[int] = None, chunk: Optional[int] = None,
                             slopes: Optional[torch.Tensor] = None, key_width: Optional[int] = None,
-                            value_width: Optional[int] = None) -> None:
-    """Attention of the step's tokens (``ctx``: cu_q, kv_len, seq_of_token) with float32 queries ``q`` [N, Hq, Dk]
-    over pools [pages, Hkv, page, stride]: keys are the first ``key_width`` (default: all) elements of a ``k_pool``
-    row, values the first ``value_width`` of a ``v_pool`` row (the two may be one tensor).  ``slopes`` [Hq] float32:
-    the score loses slopes[h] * distance.  ``window`` / ``chunk`` bound the visible keys from below."""
+                            value_width: Optional[int] = None, tiled: Optional[bool] = None) -> None:
+    """Attention of the step's tokens (``ctx``: cu_q, kv_len, seq_of_token, host.q_lens) with float32 queries ``q``
+    [N, Hq, Dk] over pools [pages, Hkv, page, stride]: keys are the first ``key_width`` (default: all) elements of a
+    ``k_pool`` row, values the first ``value_width`` of a ``v_pool`` row (the two may be one tensor).  ``slopes`` [Hq]
+    float32: the score loses slopes[h] * distance.  ``window`` / ``chunk`` bound the visible keys from below.
+    ``tiled``: None picks the tiled kernel where it applies, False forces the plain one."""
     _cuda(q, k_pool, v_pool, out, block_table, slopes)
     _check_against(k_pool)
     n, hq, dk = q.shape
@@ -893,6 +912,21 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     assert (key_width or k_stride) == dk and (value_width or v_stride) == dv and v_pool.shape[:3] == k_pool.shape[:3]
     assert block_table.dtype == torch.int32 and block_table.dim() == 2
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == hq)
+    if tiled is None:
+        tiled = GENERAL_TILED
+    if tiled and fn("pb_attention_general_tiled_supported")(code(out.dtype), _p(k_pool), _p(v_pool), hq, hkv, dk, dv, k_stride,
+                                                            v_stride):
+        group = hq // hkv
+        row_tiles = sum(-(-(int(ql) * group) // GENERAL_ROWS) for ql in ctx.host.q_lens)
+        n_splits = general_splits(row_tiles * hkv, block_table.shape[1] * page_size)
+        partial = ctx.scratch("attn.general.partial", (n * hq * n_splits * (dv + 2),), torch.float32) if n_splits > 1 else None
+        check(fn("pb_paged_attention_general_tiled")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(partial),
+                                                     _p(block_table), block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len),
+                                                     _p(slopes), n, len(ctx.host.q_lens), row_tiles, n_splits, hq, hkv, dk, dv,
+                                                     k_stride, v_stride, page_size, float(scale), int(window or 0),
+                                                     int(chunk or 0), stream()),
+              "paged_attention_general_tiled", kernels=2 if n_splits > 1 else 1)
+        return
     check(fn("pb_paged_attention_general")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
                                            block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len), _p(ctx.seq_of_token), _p(slopes),
                                            n, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale), int(window or 0),
@@ -917,11 +951,11 @@ def qkv_split_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
 
 
 def heads_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
-    """out[n, h, :] = w[h] @ a[n, h, :] for every head (float32 sums in ascending k), times sigmoid(gate[n, h, :]) where a
+    """out[n, h, :] = a[n, h, :] @ w[h] for every head (float32 sums in ascending k), times sigmoid(gate[n, h, :]) where a
     gate is given.  ``a`` [N, H, K], ``out`` [N, H, M] and ``gate`` [N, H * M] may be views whose last dimension is
-    contiguous; ``w`` [H, M, K] is contiguous.  ``out`` is float32 or of the dtype of ``a`` and ``w``."""
+    contiguous; ``w`` [H, K, M] is contiguous.  ``out`` is float32 or of the dtype of ``a`` and ``w``."""
     n, h, k = a.shape
-    h2, m, k2 = w.shape
+    h2, k2, m = w.shape
     assert (h2, k2) == (h, k) and out.shape == (n, h, m) and a.dtype == w.dtype and w.is_contiguous()
     assert a.is_cuda and w.is_cuda and out.is_cuda and a.stride(2) == 1 and out.stride(2) == 1
     g_tok = 0

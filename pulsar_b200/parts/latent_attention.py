@@ -78,9 +78,10 @@ class LatentAttention(Mixer):
         if self.gated:
             rows.append(tensors[p + nm["gate"]])
         self.w_in = torch.cat(rows, dim=0).contiguous() if len(rows) > 1 else rows[0]      # rows: q | down | gate
-        # the key expansion serves the query side transposed: [H, rank, head_dim]
-        self.w_uk_t = tensors[p + nm["up_k"]].view(s.n_heads, s.head_dim, self.rank).transpose(1, 2).contiguous()
-        self.w_uv = tensors[p + nm["up_v"]].view(s.n_heads, s.value_dim, self.rank).contiguous()
+        # per head [inputs, outputs]: the key expansion as stored serves the query side (head_dim -> rank), the value
+        # expansion is transposed once (rank -> value_dim)
+        self.w_uk_t = tensors[p + nm["up_k"]].view(s.n_heads, s.head_dim, self.rank).contiguous()
+        self.w_uv = tensors[p + nm["up_v"]].view(s.n_heads, s.value_dim, self.rank).transpose(1, 2).contiguous()
         self.w_o = tensors[p + nm["o"]]
 
     def weight_bytes(self) -> int:

@@ -271,16 +271,28 @@ def _paged(rows, page_size, order):
     return pool, torch.tensor([order[:n_pages]], dtype=torch.int32)
 
 
+def _step_context(q_lens, kv_lens):
+    """What the attention wrappers read of a step: its device arrays, the lengths on the host, scratch memory."""
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    return types.SimpleNamespace(cu_q=i32(cu), kv_len=i32(kv_lens), n_seqs=len(q_lens), host=types.SimpleNamespace(q_lens=list(q_lens)),
+                                 seq_of_token=i32([s for s, n in enumerate(q_lens) for _ in range(n)]),
+                                 scratch=lambda tag, shape, dtype=None: torch.empty(shape, dtype=dtype, device="cuda"))
+
+
 @gpu
+@pytest.mark.parametrize("tiled", [True, False])
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_one_key_that_stands_out_at_every_edge(dtype, decode):
+def test_one_key_that_stands_out_at_every_edge(dtype, decode, tiled):
     """General attention kernel: one key is made to dominate wherever it is visible.  It is put far back among hundreds, on
     both sides of a page border, and just inside and just outside the query's chunk and window; a mask that is one token
     off moves the whole output."""
     from pulsar_b200 import ops
     g = torch.Generator().manual_seed(21)
-    L, H, G, D, Dv, page, chunk, window = 389, 4, 2, 20, 12, 16, 50, 70
+    L, H, G, D, Dv, page, chunk, window = 389, 4, 2, 24, 16, 16, 50, 70
     order = list(range(40))
     random.Random(4).shuffle(order)
     slopes = plain.distance_slopes(H, torch.float64)
@@ -304,18 +316,17 @@ def test_one_key_that_stands_out_at_every_edge(dtype, decode):
         k_pool, table = _paged(k.to(dtype), page, order)
         v_pool, _ = _paged(v.to(dtype), page, order)
         n_q = 1 if decode else L
-        ctx = types.SimpleNamespace(
-            cu_q=torch.tensor([0, n_q], dtype=torch.int32).cuda(), kv_len=torch.tensor([L], dtype=torch.int32).cuda(),
-            seq_of_token=torch.zeros(n_q, dtype=torch.int32).cuda())
+        ctx = _step_context([n_q], [L])
         out = torch.empty(n_q, H, Dv, dtype=dtype, device="cuda")
         ops.paged_attention_general(ctx, q[L - n_q:].float().cuda().contiguous(), k_pool.cuda(), v_pool.cuda(), out, table.cuda(),
-                                    0.3, kw["window"], kw["chunk"], slopes.float().cuda())
+                                    0.3, kw["window"], kw["chunk"], slopes.float().cuda(), tiled=tiled)
         err = float((out.double().cpu() - want[L - n_q:]).abs().max() / want.abs().max())
         assert err < (2e-5 if dtype == torch.float32 else 1e-2), f"mask {mask}, key at {spot}: error {err:.3e}"
 
 
 @gpu
-def test_value_as_the_leading_part_of_the_key_row():
+@pytest.mark.parametrize("tiled", [True, False])
+def test_value_as_the_leading_part_of_the_key_row(tiled):
     """The layout of latent attention: one pool, the value is the first elements of the key row, one shared head."""
     from pulsar_b200 import ops
     g = torch.Generator().manual_seed(8)
@@ -326,11 +337,11 @@ def test_value_as_the_leading_part_of_the_key_row():
     q[..., 1] = 2.0
     want = plain.dense_attention(q, rows.expand(L, H, rank + rot), rows[..., :rank].expand(L, H, rank), 0.2)
     pool, table = _paged(rows.float(), page, list(reversed(range(19))))
-    ctx = types.SimpleNamespace(cu_q=torch.tensor([0, L], dtype=torch.int32).cuda(), kv_len=torch.tensor([L], dtype=torch.int32).cuda(),
-                                seq_of_token=torch.zeros(L, dtype=torch.int32).cuda())
+    ctx = _step_context([L], [L])
     out = torch.empty(L, H, rank, dtype=torch.float32, device="cuda")
     pool = pool.cuda()
-    ops.paged_attention_general(ctx, q.float().cuda(), pool, pool, out, table.cuda(), 0.2, key_width=rank + rot, value_width=rank)
+    ops.paged_attention_general(ctx, q.float().cuda(), pool, pool, out, table.cuda(), 0.2, key_width=rank + rot, value_width=rank,
+                                tiled=tiled)
     assert float((out.double().cpu() - want).abs().max()) < 2e-5
 
 
@@ -350,11 +361,12 @@ def test_small_kernels_against_their_formulas(dtype):
     wide, w, gate = rnd(n, H * (K + 6)), rnd(H, M, K), rnd(n, 5 + H * M)
     a = wide.view(n, H, K + 6)[:, :, :K]
     out = torch.zeros(n, H, M + 3, dtype=torch.float32, device="cuda")
-    ops.heads_linear(a.cuda(), w.cuda(), out[:, :, :M])
+    w_km = w.transpose(1, 2).contiguous().cuda()          # the kernel takes each head's weights [inputs, outputs]
+    ops.heads_linear(a.cuda(), w_km, out[:, :, :M])
     close(out[:, :, :M], torch.einsum("nhk,hmk->nhm", a.double(), w.double()), "heads_linear")
     assert float(out[:, :, M:].abs().max()) == 0.0
     gated = torch.empty(n, H, M, dtype=dtype, device="cuda")
-    ops.heads_linear(a.cuda(), w.cuda(), gated, gate.cuda()[:, 5:])
+    ops.heads_linear(a.cuda(), w_km, gated, gate.cuda()[:, 5:])
     close(gated, torch.einsum("nhk,hmk->nhm", a.double(), w.double()) * torch.sigmoid(gate[:, 5:].double()).view(n, H, M), "gated heads")
     # the norm behind a sublayer, the addition and the next norm in one kernel
     width = 52
