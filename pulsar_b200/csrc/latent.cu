@@ -10,8 +10,10 @@
 //                    Optionally multiplies by sigmoid(gate[n, h, :]) (an output gate) in float32.
 //   latent_prepare   per token: RMS norm of the latent part of the down projection (float32),
 //                    rotation of the shared key part at the token's position, both written to
-//                    the token's cache slot; rotation of every head's rotated query part into
-//                    the tail of its float32 query row [q_abs | q_rot].
+//                    the token's cache slot (and, where asked, to contiguous rows for the expanded form);
+//                    rotation of every head's rotated query part into its float32 query row
+//                    ([q_abs | q_rot], or [q_plain | q_rot] for the expanded form).
+//   latent_expand_keys, sigmoid_gate: the expanded form's key rows [plain | shared rotated part], and its output gate.
 // The rotation pairs neighbours: (x[2i], x[2i+1]) turns by the angle of table column i; dimensions
 // beyond the rotated ones pass unchanged.
 #include "common.cuh"
@@ -123,49 +125,90 @@ heads_linear_kernel(const T* __restrict__ a, long a_tok, int a_head, const T* __
     }
 }
 
+struct PrepareShape {
+    int H, dim, rot_dim, rot_dims, rank, page_size;
+    int q_row, q_off, copy_plain;       // rows of q_out are q_row wide; the rotated part goes to q_off; plain dimensions are copied to the front or not
+    long q_tok, down_tok;
+    float eps;
+};
+
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(const T* __restrict__ q, long q_tok, const T* __restrict__ down, long down_tok,
-                      const float* __restrict__ norm_w, float eps, const float* __restrict__ cos_t,
-                      const float* __restrict__ sin_t, const int* __restrict__ slots, T* __restrict__ pool,
-                      float* __restrict__ q_full, int H, int dim, int rot_dim, int rot_dims, int rank, int page_size,
-                      const PoolBounds bounds) {
+latent_prepare_kernel(const T* __restrict__ q, const T* __restrict__ down, const float* __restrict__ norm_w,
+                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ slots,
+                      T* __restrict__ pool, float* __restrict__ q_out, T* __restrict__ latent_out, T* __restrict__ rot_out,
+                      const PrepareShape sh, const PoolBounds bounds) {
     __shared__ float scratch[32];
     const int t = blockIdx.x;
-    const int half = rot_dims >> 1;
+    const int rank = sh.rank, rot_dim = sh.rot_dim, half = sh.rot_dims >> 1;
     const float* ct = cos_t + (size_t)t * half;
     const float* st = sin_t + (size_t)t * half;
     if (down != nullptr) {                      // uniform over the block
-        const T* x = down + (size_t)t * down_tok;
+        const T* x = down + (size_t)t * sh.down_tok;
         float ss = 0.0f;
         for (int i = threadIdx.x; i < rank; i += blockDim.x) { const float v = to_float(x[i]); ss += v * v; }
         ss = block_sum(ss, scratch);
-        const float inv = rsqrtf(ss / (float)rank + eps);
+        const float inv = rsqrtf(ss / (float)rank + sh.eps);
         const int slot = slots[t];
-        if (slot >= 0 && slot_ok(slot, page_size, bounds)) {
-            T* dst = pool + (size_t)slot * (rank + rot_dim);        // [pages, 1, page, rank + rot_dim]: slot = page * page_size + offset
-            for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_float<T>(to_float(x[i]) * inv * norm_w[i]);
-            for (int i = threadIdx.x; i < half; i += blockDim.x) {
-                const float u = to_float(x[rank + 2 * i]), v = to_float(x[rank + 2 * i + 1]);
-                dst[rank + 2 * i] = from_float<T>(u * ct[i] - v * st[i]);
-                dst[rank + 2 * i + 1] = from_float<T>(v * ct[i] + u * st[i]);
-            }
-            for (int i = rot_dims + threadIdx.x; i < rot_dim; i += blockDim.x) dst[rank + i] = x[rank + i];
+        const bool cached = slot >= 0 && slot_ok(slot, sh.page_size, bounds);
+        T* dst = pool + (size_t)(cached ? slot : 0) * (rank + rot_dim);   // [pages, 1, page, rank + rot_dim]: slot = page * page_size + offset
+        T* lat = latent_out ? latent_out + (size_t)t * rank : nullptr;
+        T* rot = rot_out ? rot_out + (size_t)t * rot_dim : nullptr;
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+            const T v = from_float<T>(to_float(x[i]) * inv * norm_w[i]);
+            if (cached) dst[i] = v;
+            if (lat) lat[i] = v;
+        }
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float u = to_float(x[rank + 2 * i]), v = to_float(x[rank + 2 * i + 1]);
+            const T a = from_float<T>(u * ct[i] - v * st[i]), b = from_float<T>(v * ct[i] + u * st[i]);
+            if (cached) { dst[rank + 2 * i] = a; dst[rank + 2 * i + 1] = b; }
+            if (rot) { rot[2 * i] = a; rot[2 * i + 1] = b; }
+        }
+        for (int i = sh.rot_dims + threadIdx.x; i < rot_dim; i += blockDim.x) {
+            if (cached) dst[rank + i] = x[rank + i];
+            if (rot) rot[i] = x[rank + i];
         }
     }
-    const int per_head = dim + rot_dim;
+    const int per_head = sh.dim + rot_dim, H = sh.H;
     for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
         const int h = i / half, j = i % half;
-        const T* src = q + (size_t)t * q_tok + (size_t)h * per_head + dim;
-        float* dst = q_full + ((size_t)t * H + h) * (rank + rot_dim) + rank;
+        const T* src = q + (size_t)t * sh.q_tok + (size_t)h * per_head + sh.dim;
+        float* dst = q_out + ((size_t)t * H + h) * sh.q_row + sh.q_off;
         const float u = to_float(src[2 * j]), v = to_float(src[2 * j + 1]);
         dst[2 * j] = u * ct[j] - v * st[j];
         dst[2 * j + 1] = v * ct[j] + u * st[j];
     }
-    const int rest = rot_dim - rot_dims;
+    const int rest = rot_dim - sh.rot_dims;
     for (int i = threadIdx.x; i < H * rest; i += blockDim.x) {
-        const int h = i / rest, j = rot_dims + i % rest;
-        q_full[((size_t)t * H + h) * (rank + rot_dim) + rank + j] = to_float(q[(size_t)t * q_tok + (size_t)h * per_head + dim + j]);
+        const int h = i / rest, j = sh.rot_dims + i % rest;
+        q_out[((size_t)t * H + h) * sh.q_row + sh.q_off + j] = to_float(q[(size_t)t * sh.q_tok + (size_t)h * per_head + sh.dim + j]);
+    }
+    if (sh.copy_plain) {
+        for (int i = threadIdx.x; i < H * sh.dim; i += blockDim.x) {
+            const int h = i / sh.dim, j = i % sh.dim;
+            q_out[((size_t)t * H + h) * sh.q_row + j] = to_float(q[(size_t)t * sh.q_tok + (size_t)h * per_head + j]);
+        }
+    }
+}
+
+// keys[n, h, :] = [plain[n, h, :dim] | shared[n, :rot_dim]]: every head's expanded plain key beside the rotated part all heads share.
+template <typename T>
+__global__ void latent_expand_keys_kernel(const T* __restrict__ plain, const T* __restrict__ shared, T* __restrict__ keys, int H,
+                                          int dim, int rot_dim) {
+    const int t = blockIdx.x, row = dim + rot_dim;
+    for (int i = threadIdx.x; i < H * row; i += blockDim.x) {
+        const int h = i / row, j = i % row;
+        keys[(size_t)t * H * row + i] = j < dim ? plain[((size_t)t * H + h) * dim + j] : shared[(size_t)t * rot_dim + j - dim];
+    }
+}
+
+// x[n, c] *= sigmoid(gate[n, c]) with float32 arithmetic; gate rows g_tok apart.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, long g_tok, int width, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / width, c = i % width;
+        x[i] = from_float<T>(to_float(x[i]) / (1.0f + expf(-to_float(gate[n * g_tok + c]))));
     }
 }
 
@@ -206,23 +249,52 @@ PB_EXPORT int pb_heads_linear(int dtype, int out_dtype, const void* a, long a_to
 
 // q: the projected query rows, head h at q + n * q_tok + h * (dim + rot_dim), its rotated part behind `dim` plain
 // dimensions.  down (may be null: the layer borrows another layer's cache): rows of rank + rot_dim at n * down_tok.
-// pool [pages, 1, page_size, rank + rot_dim]; q_full float32 [N, H, rank + rot_dim] (only the tail is written).
+// pool [pages, 1, page_size, rank + rot_dim].  q_out float32 [N, H, q_row]: every head's rotated part, turned, at q_off;
+// with copy_plain its plain dimensions at 0.  latent_out [N, rank] / rot_out [N, rot_dim] (may be null): what went to the cache.
 PB_EXPORT int pb_latent_prepare(int dtype, const void* q, long q_tok, const void* down, long down_tok, const float* norm_w,
-                                float eps, const float* cos_t, const float* sin_t, const int* slots, void* pool, float* q_full,
-                                int N, int H, int dim, int rot_dim, int rot_dims, int rank, int page_size, cudaStream_t stream) {
+                                float eps, const float* cos_t, const float* sin_t, const int* slots, void* pool, float* q_out,
+                                int q_row, int q_off, int copy_plain, void* latent_out, void* rot_out, int N, int H, int dim,
+                                int rot_dim, int rot_dims, int rank, int page_size, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (H <= 0 || dim < 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || rot_dims % 2 || rank <= 0 || page_size <= 0)
+    if (H <= 0 || dim < 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || rot_dims % 2 || rank <= 0 || page_size <= 0 ||
+        q_off < 0 || q_off + rot_dim > q_row || (copy_plain && dim > q_off))
         return PB_ERR_BAD_SIZE;
     if (down != nullptr && (norm_w == nullptr || slots == nullptr || pool == nullptr)) return PB_ERR_BAD_SIZE;
+    const PrepareShape sh{H, dim, rot_dim, rot_dims, rank, page_size, q_row, q_off, copy_plain, q_tok, down_tok, eps};
     if (dtype == PB_F32)
-        latent_prepare_kernel<float><<<N, 128, 0, stream>>>((const float*)q, q_tok, (const float*)down, down_tok, norm_w, eps, cos_t,
-                                                            sin_t, slots, (float*)pool, q_full, H, dim, rot_dim, rot_dims, rank,
-                                                            page_size, pb::pool_bounds_now());
+        latent_prepare_kernel<float><<<N, 128, 0, stream>>>((const float*)q, (const float*)down, norm_w, cos_t, sin_t, slots,
+                                                            (float*)pool, q_out, (float*)latent_out, (float*)rot_out, sh,
+                                                            pb::pool_bounds_now());
     else if (dtype == PB_BF16)
-        latent_prepare_kernel<__nv_bfloat16><<<N, 128, 0, stream>>>((const __nv_bfloat16*)q, q_tok, (const __nv_bfloat16*)down,
-                                                                    down_tok, norm_w, eps, cos_t, sin_t, slots, (__nv_bfloat16*)pool,
-                                                                    q_full, H, dim, rot_dim, rot_dims, rank, page_size,
+        latent_prepare_kernel<__nv_bfloat16><<<N, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)down, norm_w, cos_t,
+                                                                    sin_t, slots, (__nv_bfloat16*)pool, q_out,
+                                                                    (__nv_bfloat16*)latent_out, (__nv_bfloat16*)rot_out, sh,
                                                                     pb::pool_bounds_now());
+    else return PB_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+PB_EXPORT int pb_latent_expand_keys(int dtype, const void* plain, const void* shared, void* keys, int N, int H, int dim, int rot_dim,
+                                    cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (H <= 0 || dim < 0 || rot_dim < 0 || dim + rot_dim <= 0) return PB_ERR_BAD_SIZE;
+    if (dtype == PB_F32)
+        latent_expand_keys_kernel<float><<<N, 256, 0, stream>>>((const float*)plain, (const float*)shared, (float*)keys, H, dim, rot_dim);
+    else if (dtype == PB_BF16)
+        latent_expand_keys_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>((const __nv_bfloat16*)plain, (const __nv_bfloat16*)shared,
+                                                                        (__nv_bfloat16*)keys, H, dim, rot_dim);
+    else return PB_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+PB_EXPORT int pb_sigmoid_gate(int dtype, void* x, const void* gate, long g_tok, int N, int width, cudaStream_t stream) {
+    if (N <= 0 || width <= 0) return 0;
+    const size_t total = (size_t)N * width;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == PB_F32) sigmoid_gate_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)x, (const float*)gate, g_tok, width, total);
+    else if (dtype == PB_BF16)
+        sigmoid_gate_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)gate, g_tok, width, total);
     else return PB_ERR_BAD_DTYPE;
     return launch_status();
 }

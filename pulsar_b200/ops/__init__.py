@@ -88,7 +88,9 @@ _SIGNATURES = {
     "pb_paged_attention_general_tiled": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_qkv_split_write": [_I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "pb_heads_linear": [_I, _I, _P, _L, _I, _P, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
-    "pb_latent_prepare": [_I, _P, _L, _P, _L, _P, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "pb_latent_prepare": [_I, _P, _L, _P, _L, _P, _F, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "pb_latent_expand_keys": [_I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "pb_sigmoid_gate": [_I, _P, _P, _L, _I, _I, _P],
     "pb_causal_conv_silu": [_I, _P, _L, _P, _P, _P, _L, _L, _P, _P, _P, _P, _I, _I, _I, _P],
     "pb_selective_scan": [_I, _P, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "pb_post_norm_add": [_I, _P, _P, _P, _F, _P, _F, _P, _I, _I, _P],
@@ -101,7 +103,7 @@ _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk
               "paged_attention_decode_tc_qkv",
               "paged_attention_prefill_tc", "paged_attention_prefill_tcgen05", "gemm_skinny", "gemm_skinny_accumulate",
               "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update",
-              "paged_attention_general", "paged_attention_general_tiled", "qkv_split_write", "heads_linear", "latent_prepare", "causal_conv_silu",
+              "paged_attention_general", "paged_attention_general_tiled", "qkv_split_write", "heads_linear", "latent_prepare", "latent_expand_keys", "sigmoid_gate", "causal_conv_silu",
               "selective_scan", "post_norm_add", "clamped_glu"}
 
 
@@ -968,15 +970,19 @@ def heads_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Opti
 
 def latent_prepare(q: torch.Tensor, down: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float,
                    cos: torch.Tensor, sin: torch.Tensor, slots: Optional[torch.Tensor], pool: Optional[torch.Tensor],
-                   q_full: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, page_size: int) -> None:
+                   q_out: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, page_size: int,
+                   plain_too: bool = False, latent_out: Optional[torch.Tensor] = None,
+                   rot_out: Optional[torch.Tensor] = None) -> None:
     """Per token: where ``down`` [N, rank + rot_dim] is given, its latent part RMS-normed with ``norm_weight`` and its
-    rotated part turned at the token's position go to the token's slot of ``pool`` [pages, 1, page, rank + rot_dim];
-    every head's rotated query part (behind ``dim`` plain dimensions of a ``q`` row) goes, turned, to the tail of
-    ``q_full`` float32 [N, H, rank + rot_dim].  ``q`` and ``down`` may be column slices of one tensor.  The rotation
-    pairs neighbours; ``cos`` / ``sin`` [N, rotated dims / 2]."""
+    rotated part turned at the token's position go to the token's slot of ``pool`` [pages, 1, page, rank + rot_dim] (and to
+    ``latent_out`` [N, rank] / ``rot_out`` [N, rot_dim] where given); every head's rotated query part (behind ``dim`` plain
+    dimensions of a ``q`` row) goes, turned, to the tail of its row of ``q_out`` float32 [N, H, row]: row = rank + rot_dim,
+    or with ``plain_too`` row = dim + rot_dim with the plain dimensions copied to the front.  ``q`` and ``down`` may be column
+    slices of one tensor.  The rotation pairs neighbours; ``cos`` / ``sin`` [N, rotated dims / 2]."""
     n = q.shape[0]
+    front = dim if plain_too else rank
     assert q.is_cuda and q.stride(1) == 1 and q.shape[1] == n_heads * (dim + rot_dim)
-    assert q_full.dtype == torch.float32 and q_full.is_contiguous() and q_full.shape == (n, n_heads, rank + rot_dim)
+    assert q_out.dtype == torch.float32 and q_out.is_contiguous() and q_out.shape == (n, n_heads, front + rot_dim)
     assert cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[0] == n and cos.is_contiguous()
     rot_dims = 2 * cos.shape[1]
     down_tok = 0
@@ -986,9 +992,32 @@ def latent_prepare(q: torch.Tensor, down: Optional[torch.Tensor], norm_weight: O
         assert pool.dtype == q.dtype and pool.is_contiguous() and pool.shape[1:] == (1, page_size, rank + rot_dim)
         _check_against(pool)
         down_tok = down.stride(0)
+        for t, width in ((latent_out, rank), (rot_out, rot_dim)):
+            assert t is None or (t.dtype == q.dtype and t.is_contiguous() and t.shape == (n, width) and t.is_cuda)
+    else:
+        assert latent_out is None and rot_out is None
     check(fn("pb_latent_prepare")(code(q.dtype), _p(q), q.stride(0), _p(down), down_tok, _p(norm_weight), float(eps), _p(cos),
-                                  _p(sin), _p(slots), _p(pool), _p(q_full), n, n_heads, dim, rot_dim, rot_dims, rank, page_size,
-                                  stream()), "latent_prepare")
+                                  _p(sin), _p(slots), _p(pool), _p(q_out), front + rot_dim, front, 1 if plain_too else 0,
+                                  _p(latent_out), _p(rot_out), n, n_heads, dim, rot_dim, rot_dims, rank, page_size, stream()),
+          "latent_prepare")
+
+
+def latent_expand_keys(plain: torch.Tensor, shared: torch.Tensor, keys: torch.Tensor) -> None:
+    """keys[n, h, :] = [plain[n, h, :] | shared[n, :]]: every head's expanded key beside the rotated part all heads share."""
+    _cuda(plain, shared, keys)
+    n, h, dim = plain.shape
+    rot_dim = shared.shape[1]
+    assert shared.shape[0] == n and keys.shape == (n, h, dim + rot_dim) and plain.dtype == shared.dtype == keys.dtype
+    check(fn("pb_latent_expand_keys")(code(keys.dtype), _p(plain), _p(shared), _p(keys), n, h, dim, rot_dim, stream()),
+          "latent_expand_keys")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x[n, :] *= sigmoid(gate[n, :]) in place (float32 arithmetic); ``gate`` may be a column slice."""
+    _cuda(x)
+    n, width = x.shape
+    assert gate.is_cuda and gate.dtype == x.dtype and gate.shape == (n, width) and gate.stride(1) == 1
+    check(fn("pb_sigmoid_gate")(code(x.dtype), _p(x), _p(gate), gate.stride(0), n, width, stream()), "sigmoid_gate")
 
 
 # ---------------------------------------------------------------- selective scan

@@ -1,6 +1,7 @@
 """Attention over a compressed latent: one cached row per token, expanded per head on the fly."""
 from __future__ import annotations
 
+import os
 from typing import Dict, List
 
 import torch
@@ -10,6 +11,9 @@ from ..cache.manager import CachedTensor, CacheNeed
 from ..config.registry import MIXERS, POSITIONS
 from ..config.specs import MixerSpec
 from .base import CacheView, Mixer, StepContext, WeightSpec
+
+# PULSAR_LATENT_EXPAND=0: whole prompts too take the absorbed form.
+EXPAND_PROMPTS = os.environ.get("PULSAR_LATENT_EXPAND", "1") != "0"
 
 
 @MIXERS.register("latent_attention")
@@ -23,7 +27,8 @@ class LatentAttention(Mixer):
     (q_abs[h] . c + q_rot[h] . key_rot) * scale, and the head's output is W_uv[h] (sum_j p_j c_j).  So the attention
     itself runs with one shared key/value head over the cached rows (key = the whole row, value = its first
     ``kv_rank`` elements) and the two expansions become per-head products on the query and on the output side
-    (``ops.heads_linear``).  Queries stay float32 from their rotation to the scores.
+    (``ops.heads_linear``).  Queries stay float32 from their rotation to the scores.  A step of whole prompts, whose
+    keys are all among its own tokens, expands them instead (see ``forward``); the two forms compute the same function.
 
     Options (``spec.extra``): ``kv_rank``, ``rot_dim``, ``latent_norm_eps``, ``gated`` (the concatenated heads are
     multiplied by sigmoid(W_g h), h the mixer's input).  ``spec.position`` gives the rotation (its table's
@@ -49,7 +54,7 @@ class LatentAttention(Mixer):
                                                  ("latent_norm", "kv_norm.weight"), ("up_k", "k_up_proj.weight"),
                                                  ("up_v", "v_up_proj.weight"), ("gate", "gate_proj.weight"),
                                                  ("o", "o_proj.weight"))}
-        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.latent_norm = None
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.latent_norm = self.w_uk_rows = self.w_uv_rows = None
 
     @property
     def row(self) -> int:
@@ -82,10 +87,11 @@ class LatentAttention(Mixer):
         # expansion is transposed once (rank -> value_dim)
         self.w_uk_t = tensors[p + nm["up_k"]].view(s.n_heads, s.head_dim, self.rank).contiguous()
         self.w_uv = tensors[p + nm["up_v"]].view(s.n_heads, s.value_dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uk_rows, self.w_uv_rows = tensors[p + nm["up_k"]], tensors[p + nm["up_v"]]      # as stored: the expanded form's products
         self.w_o = tensors[p + nm["o"]]
 
     def weight_bytes(self) -> int:
-        ts = [self.w_in, self.w_uk_t, self.w_uv, self.w_o, self.latent_norm]
+        ts = [self.w_in, self.w_uk_t, self.w_uv, self.w_o, self.latent_norm]      # a step reads one form of the expansions
         return sum(t.numel() * t.element_size() for t in ts if t is not None)
 
     def cache_need(self) -> CacheNeed:
@@ -100,13 +106,30 @@ class LatentAttention(Mixer):
         q = proj[:, :q_width]
         down = proj[:, q_width:q_width + self.row] if s.own_kv else None
         gate = proj[:, self.w_in.shape[0] - H * s.value_dim:] if self.gated else None
-        pool = cache.pools["latent"]
-        q_full = ctx.scratch("latent.q", (n, H, self.row), torch.float32)
-        ops.heads_linear(q.view(n, H, s.head_dim + self.rot_dim)[:, :, :s.head_dim], self.w_uk_t, q_full[:, :, :self.rank])
         if self.position is not None:
             cos, sin = self.position.tables(ctx)
         else:
             cos = sin = ctx.scratch("latent.norope", (n, 0), torch.float32)
+        # A step that brings only whole prompts (every sequence starts at 0) has all its keys among its own tokens: it
+        # expands them once (two products for the step) and attends with keys head_dim + rot_dim wide and values value_dim
+        # wide, a third of the absorbed form's arithmetic per (query, key) pair.  Every other step (portions behind a
+        # cached part, single tokens) attends over the cached rows in the absorbed form.  A captured step is a step of
+        # single tokens and always takes the absorbed form, so nothing here goes stale in a replay.
+        if EXPAND_PROMPTS and not ctx.all_decode and s.window is None and all(start == 0 for start in ctx.host.starts):
+            heads = self._expanded(ctx, q, down, cos, sin, cache)
+            if gate is not None:
+                ops.sigmoid_gate(heads.view(n, H * s.value_dim), gate)
+        else:
+            heads = self._absorbed(ctx, q, down, gate, cos, sin, cache)
+        out = ctx.scratch("latent.out", (n, s.hidden))
+        ops.linear(heads.view(n, H * s.value_dim), self.w_o, out)
+        return out
+
+    def _absorbed(self, ctx, q, down, gate, cos, sin, cache) -> torch.Tensor:
+        s, n, H = self.spec, ctx.n_tokens, self.spec.n_heads
+        pool = cache.pools["latent"]
+        q_full = ctx.scratch("latent.q", (n, H, self.row), torch.float32)
+        ops.heads_linear(q.view(n, H, s.head_dim + self.rot_dim)[:, :, :s.head_dim], self.w_uk_t, q_full[:, :, :self.rank])
         ops.latent_prepare(q, down, self.latent_norm, self.norm_eps, cos, sin, cache.slots if s.own_kv else None,
                            pool if s.own_kv else None, q_full, H, s.head_dim, self.rot_dim, self.rank, cache.page_size)
         mixed = ctx.scratch("latent.mixed", (n, H, self.rank))
@@ -114,6 +137,35 @@ class LatentAttention(Mixer):
                                     key_width=self.row, value_width=self.rank)
         heads = ctx.scratch("latent.heads", (n, H, s.value_dim))
         ops.heads_linear(mixed, self.w_uv, heads, gate)
-        out = ctx.scratch("latent.out", (n, s.hidden))
-        ops.linear(heads.view(n, H * s.value_dim), self.w_o, out)
-        return out
+        return heads
+
+    def _expanded(self, ctx, q, down, cos, sin, cache) -> torch.Tensor:
+        s, n, H = self.spec, ctx.n_tokens, self.spec.n_heads
+        pool = cache.pools["latent"]
+        key = ("latent.rows", pool.data_ptr())            # what the cache's owner wrote this step, for those who borrow it
+        q_cat = ctx.scratch("latent.q", (n, H, s.head_dim + self.rot_dim), torch.float32)
+        if s.own_kv:
+            latent = ctx.scratch(f"latent.rows.{pool.data_ptr()}", (n, self.rank))
+            shared = ctx.scratch(f"latent.rot.{pool.data_ptr()}", (n, self.rot_dim))
+            ops.latent_prepare(q, down, self.latent_norm, self.norm_eps, cos, sin, cache.slots, pool, q_cat, H, s.head_dim,
+                               self.rot_dim, self.rank, cache.page_size, plain_too=True, latent_out=latent, rot_out=shared)
+            ctx.shared[key] = (latent, shared)
+        else:
+            latent, shared = ctx.shared[key]
+            ops.latent_prepare(q, None, None, self.norm_eps, cos, sin, None, None, q_cat, H, s.head_dim, self.rot_dim, self.rank,
+                               cache.page_size, plain_too=True)
+        k_plain = ctx.scratch("latent.k_plain", (n, H * s.head_dim))
+        ops.linear(latent, self.w_uk_rows, k_plain)
+        values = ctx.scratch("latent.values", (n, H * s.value_dim))
+        ops.linear(latent, self.w_uv_rows, values)
+        keys = ctx.scratch("latent.keys", (n, H, s.head_dim + self.rot_dim))
+        ops.latent_expand_keys(k_plain.view(n, H, s.head_dim), shared, keys)
+        # the step's own rows as pages of one token: row t of sequence i is page cu_q[i] + t
+        table = ctx.shared.get("rows_as_pages")
+        if table is None:
+            table = (ctx.cu_q[:-1, None] + torch.arange(ctx.max_q_len, dtype=torch.int32, device=ctx.device)[None, :]).contiguous()
+            ctx.shared["rows_as_pages"] = table
+        heads = ctx.scratch("latent.heads", (n, H, s.value_dim))
+        ops.paged_attention_general(ctx, q_cat, keys.view(n, H, 1, s.head_dim + self.rot_dim), values.view(n, H, 1, s.value_dim),
+                                    heads, table, s.scale, None, s.chunk, None)
+        return heads
