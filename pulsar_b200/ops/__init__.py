@@ -86,6 +86,9 @@ _SIGNATURES = {
     "pb_paged_attention_general": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_attention_general_tiled_supported": [_I, _P, _P, _I, _I, _I, _I, _I, _I],
     "pb_paged_attention_general_tiled": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "pb_attention_general_tc_tile": [],
+    "pb_attention_general_tc_supported": [_I, _P, _P, _P, _I, _I, _I, _I, _I, _I],
+    "pb_paged_attention_general_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_qkv_split_write": [_I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "pb_heads_linear": [_I, _I, _P, _L, _I, _P, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
     "pb_latent_prepare": [_I, _P, _L, _P, _L, _P, _F, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -103,7 +106,7 @@ _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk
               "paged_attention_decode_tc_qkv",
               "paged_attention_prefill_tc", "paged_attention_prefill_tcgen05", "gemm_skinny", "gemm_skinny_accumulate",
               "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update",
-              "paged_attention_general", "paged_attention_general_tiled", "qkv_split_write", "heads_linear", "latent_prepare", "latent_expand_keys", "sigmoid_gate", "causal_conv_silu",
+              "paged_attention_general", "paged_attention_general_tiled", "paged_attention_general_tc", "qkv_split_write", "heads_linear", "latent_prepare", "latent_expand_keys", "sigmoid_gate", "causal_conv_silu",
               "selective_scan", "post_norm_add", "clamped_glu"}
 
 
@@ -884,6 +887,11 @@ def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, wind
 # plain one (a block per token and head) for every other size.  PULSAR_GENERAL_TILED=0 leaves the tiled one out.
 GENERAL_TILED = os.environ.get("PULSAR_GENERAL_TILED", "1") != "0"
 GENERAL_ROWS = 16
+# Steps with portions of GENERAL_TC_MIN tokens or more, on bfloat16 pages with (key, value) widths (64, 64), (128, 128) or
+# (192, 128), take the tensor-core kernel, which splits queries and softmax weights into two bfloat16 halves each.
+# PULSAR_GENERAL_TC=0 leaves it out.
+GENERAL_TC = os.environ.get("PULSAR_GENERAL_TC", "1") != "0"
+GENERAL_TC_MIN = 16
 
 
 def general_splits(blocks: int, table_tokens: int) -> int:
@@ -898,12 +906,14 @@ def general_splits(blocks: int, table_tokens: int) -> int:
 def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                             block_table: torch.Tensor, scale: float, window: Optional[int] = None, chunk: Optional[int] = None,
                             slopes: Optional[torch.Tensor] = None, key_width: Optional[int] = None,
-                            value_width: Optional[int] = None, tiled: Optional[bool] = None) -> None:
+                            value_width: Optional[int] = None, tiled: Optional[bool] = None,
+                            tensor_cores: Optional[bool] = None) -> None:
     """Attention of the step's tokens (``ctx``: cu_q, kv_len, seq_of_token, host.q_lens) with float32 queries ``q``
     [N, Hq, Dk] over pools [pages, Hkv, page, stride]: keys are the first ``key_width`` (default: all) elements of a
     ``k_pool`` row, values the first ``value_width`` of a ``v_pool`` row (the two may be one tensor).  ``slopes`` [Hq]
     float32: the score loses slopes[h] * distance.  ``window`` / ``chunk`` bound the visible keys from below.
-    ``tiled``: None picks the tiled kernel where it applies, False forces the plain one."""
+    ``tiled``: None picks the tiled kernel where it applies, False forces the plain one.  ``tensor_cores``: None picks the
+    tensor-core kernel for steps with portions where it applies, False never, True insists."""
     _cuda(q, k_pool, v_pool, out, block_table, slopes)
     _check_against(k_pool)
     n, hq, dk = q.shape
@@ -914,6 +924,20 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     assert (key_width or k_stride) == dk and (value_width or v_stride) == dv and v_pool.shape[:3] == k_pool.shape[:3]
     assert block_table.dtype == torch.int32 and block_table.dim() == 2
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == hq)
+    q_lens = ctx.host.q_lens
+    if tensor_cores is None:
+        tensor_cores = GENERAL_TC and max(q_lens) >= GENERAL_TC_MIN
+    if tensor_cores:
+        fits = fn("pb_attention_general_tc_supported")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), hq, hkv, dk, dv, k_stride,
+                                                       v_stride)
+        if fits:
+            rows = fn("pb_attention_general_tc_tile")()
+            n_q_tiles = sum(-(-int(ql) // rows) for ql in q_lens)
+            check(fn("pb_paged_attention_general_tc")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
+                                                      block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len), _p(slopes), len(q_lens),
+                                                      n_q_tiles, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale),
+                                                      int(window or 0), int(chunk or 0), stream()), "paged_attention_general_tc")
+            return
     if tiled is None:
         tiled = GENERAL_TILED
     if tiled and fn("pb_attention_general_tiled_supported")(code(out.dtype), _p(k_pool), _p(v_pool), hq, hkv, dk, dv, k_stride,

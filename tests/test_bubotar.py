@@ -325,6 +325,63 @@ def test_one_key_that_stands_out_at_every_edge(dtype, decode, tiled):
 
 
 @gpu
+@pytest.mark.parametrize("dims", [(64, 64), (128, 128), (192, 128)])
+def test_tensor_core_kernel_keeps_scores_and_weights_at_float32(dims):
+    """The tensor-core form of the general attention (bfloat16 pages, float32 queries split into two halves) against the
+    plain one in float64: two sequences of unequal length with cached parts, grouped heads, one dominant key per mask at
+    the edges of chunk, window and page.  The bar is far below one bfloat16 rounding of a query or of a softmax weight."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(33)
+    D, Dv = dims
+    H, G, page, chunk, window = 4, 2, 8, 70, 45
+    lens, starts = [233, 97], [40, 0]                     # the first sequence has 40 tokens in the cache already
+    order = list(range(64))
+    random.Random(6).shuffle(order)
+    slopes = plain.distance_slopes(H, torch.float64)
+    for mask, spot in (("none", 5), ("chunk", 139), ("chunk", 140), ("window", 187), ("window", 188), ("none", 231), ("chunk", 64)):
+        qs, ks, vs, wants = [], [], [], []
+        for L, start in zip(lens, starts):
+            q = torch.randn(L, H, D, generator=g, dtype=torch.float64)
+            k = torch.randn(L, G, D, generator=g, dtype=torch.float64)
+            v = torch.randn(L, G, Dv, generator=g, dtype=torch.float64)
+            q[..., 0] = 3.0
+            if spot < L:
+                k[spot, :, 0] = 40.0
+            k, v = k.to(torch.bfloat16).double(), v.to(torch.bfloat16).double()
+            q = q.float().double()
+            kw = dict(chunk=chunk if mask == "chunk" else None, window=window if mask == "window" else None)
+            want = plain.dense_attention(q[start:], k.repeat_interleave(H // G, 1), v.repeat_interleave(H // G, 1), 0.11, slopes,
+                                         first=start, **kw)
+            qs.append(q[start:]); ks.append(k); vs.append(v); wants.append(want)
+        # both sequences in one pool: the second one's pages follow the first one's in a shuffled order
+        n_pages = [-(-L // page) for L in lens]
+        k_pool = torch.zeros(64, G, page, D, dtype=torch.bfloat16)
+        v_pool = torch.zeros(64, G, page, Dv, dtype=torch.bfloat16)
+        table = torch.zeros(2, max(n_pages), dtype=torch.int32)
+        at = 0
+        for s, L in enumerate(lens):
+            for lp in range(n_pages[s]):
+                pid = order[at]; at += 1
+                table[s, lp] = pid
+                part_k, part_v = ks[s][lp * page:(lp + 1) * page], vs[s][lp * page:(lp + 1) * page]
+                k_pool[pid, :, :part_k.shape[0]] = part_k.transpose(0, 1).to(torch.bfloat16)
+                v_pool[pid, :, :part_v.shape[0]] = part_v.transpose(0, 1).to(torch.bfloat16)
+        ctx = _step_context([L - st for L, st in zip(lens, starts)], lens)
+        q_all = torch.cat(qs).float().cuda().contiguous()
+        out = torch.empty(q_all.shape[0], H, Dv, dtype=torch.bfloat16, device="cuda")
+        ops.paged_attention_general(ctx, q_all, k_pool.cuda(), v_pool.cuda(), out, table.cuda(), 0.11, kw["window"], kw["chunk"],
+                                    slopes.float().cuda(), tensor_cores=True)
+        want = torch.cat(wants)
+        err = float((out.double().cpu() - want).abs().max() / want.abs().max())
+        assert err < 6e-3, f"mask {mask}, key at {spot}: error {err:.3e}"          # the output's own bfloat16 rounding: 4e-3
+        # against the CUDA-core kernel, which is float32 throughout, the two agree to the output's rounding
+        ref = torch.empty_like(out)
+        ops.paged_attention_general(ctx, q_all, k_pool.cuda(), v_pool.cuda(), ref, table.cuda(), 0.11, kw["window"], kw["chunk"],
+                                    slopes.float().cuda(), tensor_cores=False)
+        assert float((out.float() - ref.float()).abs().max() / want.abs().max()) < 8e-3
+
+
+@gpu
 @pytest.mark.parametrize("tiled", [True, False])
 def test_value_as_the_leading_part_of_the_key_row(tiled):
     """The layout of latent attention: one pool, the value is the first elements of the key row, one shared head."""
