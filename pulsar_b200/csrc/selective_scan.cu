@@ -163,6 +163,141 @@ selective_scan_kernel(const T* __restrict__ x, const T* __restrict__ xz, const T
     }
 }
 
+// The scan for prompt portions: the step sizes before their bias and softplus come from a product of their own
+// (dt_pre [N, inner] float32), and the tokens of a staged round are taken four at a time: what does not depend on the
+// state (softplus, the decays' exponentials) is computed for the four first, so that only the multiply-adds of the
+// state chain from token to token, and the four sums over the state are reduced side by side.  SPL: states per lane.
+template <typename T, int G, int SPL>
+__global__ void __launch_bounds__(128)
+selective_scan_prompt_kernel(const T* __restrict__ x, const T* __restrict__ xz, const T* __restrict__ bc, long bc_tok,
+                             const float* __restrict__ dt_pre, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                             const float* __restrict__ d_skip, float* __restrict__ arena, T* __restrict__ y,
+                             const int* __restrict__ cu_q, const int* __restrict__ state_slots, const ScanShape sh) {
+    constexpr int CH = 128 / G;
+    constexpr int U = 4;
+    extern __shared__ float smem[];
+    const int S = sh.n_state, inner = sh.inner;
+    float* bc_s = smem;                               // [kStage][2 * S]
+    float* x_s = bc_s + kStage * 2 * S;               // [kStage][CH]
+    float* z_s = x_s + kStage * CH;                   // [kStage][CH]
+    float* dt_s = z_s + kStage * CH;                  // [kStage][CH]
+
+    const int seq = blockIdx.x;
+    const int group = threadIdx.x / G, gl = threadIdx.x % G;
+    const int c0 = blockIdx.y * CH;
+    const int c = c0 + group;
+    const bool live = c < inner;
+    const int q0 = cu_q[seq], q_len = cu_q[seq + 1] - q0;
+    float* slot = arena + (size_t)state_slots[seq] * sh.slot_stride;
+
+    float a[SPL], st[SPL];
+#pragma unroll
+    for (int j = 0; j < SPL; ++j) {
+        const int n = gl + G * j;
+        const bool on = live && n < S;
+        a[j] = on ? -expf(a_log[(size_t)c * S + n]) : 0.0f;
+        st[j] = on ? slot[(size_t)c * S + n] : 0.0f;
+    }
+    const float bias = live ? dt_bias[c] : 0.0f;
+    const float skip = live ? d_skip[c] : 0.0f;
+
+    for (int base = 0; base < q_len; base += kStage) {
+        const int nt = min(kStage, q_len - base);
+        __syncthreads();
+        for (int i = threadIdx.x; i < kStage * 2 * S; i += blockDim.x) {
+            const int tt = i / (2 * S), k = i % (2 * S);
+            bc_s[i] = tt < nt ? to_float(bc[(size_t)(q0 + base + tt) * bc_tok + k]) : 0.0f;
+        }
+        for (int i = threadIdx.x; i < kStage * CH; i += blockDim.x) {
+            const int tt = i / CH, k = i % CH;
+            const bool on = tt < nt && c0 + k < inner;
+            const size_t row = (size_t)(q0 + base + (on ? tt : 0));
+            x_s[i] = on ? to_float(x[row * inner + c0 + k]) : 0.0f;
+            z_s[i] = on ? to_float(xz[row * sh.xz_tok + inner + c0 + k]) : 0.0f;
+            dt_s[i] = on ? dt_pre[row * inner + c0 + k] : 0.0f;
+        }
+        __syncthreads();
+        for (int t0 = 0; t0 < nt; t0 += U) {
+            float dx[U], da[U][SPL], part[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float dt = softplus_f(dt_s[(t0 + u) * CH + group] + bias);
+                dx[u] = dt * x_s[(t0 + u) * CH + group];
+#pragma unroll
+                for (int j = 0; j < SPL; ++j) da[u][j] = expf(dt * a[j]);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float* bt = bc_s + (t0 + u) * 2 * S;
+                const bool in = t0 + u < nt;                       // the rows behind the round's end hold zeros and must not move the state
+                float p = 0.0f;
+#pragma unroll
+                for (int j = 0; j < SPL; ++j) {
+                    const int n = gl + G * j;
+                    if (n < S) {
+                        const float next = fmaf(da[u][j], st[j], dx[u] * bt[n]);
+                        st[j] = in ? next : st[j];
+                        p = fmaf(next, bt[S + n], p);
+                    }
+                }
+                part[u] = p;
+            }
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1)
+#pragma unroll
+                for (int u = 0; u < U; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], o);
+            if (live && gl < U && t0 + gl < nt) {
+                float mine = part[0];
+#pragma unroll
+                for (int u = 1; u < U; ++u) mine = (gl == u) ? part[u] : mine;
+                const int tt = t0 + gl;
+                y[(size_t)(q0 + base + tt) * inner + c] =
+                    from_float<T>((mine + skip * x_s[tt * CH + group]) * silu_f(z_s[tt * CH + group]));
+            }
+        }
+    }
+    if (!live) return;
+#pragma unroll
+    for (int j = 0; j < SPL; ++j) {
+        const int n = gl + G * j;
+        if (n < S) slot[(size_t)c * S + n] = st[j];
+    }
+    if (gl == 0) {
+        float* tail = slot + sh.tail_offset + (size_t)c * (sh.n_taps - 1);
+        for (int k = 0; k < sh.n_taps - 1; ++k) {
+            const int j = q_len - (sh.n_taps - 1) + k;
+            tail[k] = j >= 0 ? to_float(xz[(size_t)(q0 + j) * sh.xz_tok + c]) : tail[k + q_len];
+        }
+    }
+}
+
+template <typename T, int G, int SPL>
+int launch_scan_prompt(const void* x, const void* xz, const void* bc, long bc_tok, const float* dt_pre, const float* dt_bias,
+                       const float* a_log, const float* d_skip, float* arena, void* y, const int* cu_q, const int* state_slots,
+                       int n_seqs, const ScanShape& sh, cudaStream_t stream) {
+    constexpr int CH = 128 / G;
+    const size_t smem = sizeof(float) * kStage * (2 * sh.n_state + 3 * CH);
+    dim3 grid(n_seqs, (sh.inner + CH - 1) / CH);
+    selective_scan_prompt_kernel<T, G, SPL><<<grid, 128, smem, stream>>>((const T*)x, (const T*)xz, (const T*)bc, bc_tok, dt_pre, dt_bias,
+                                                                         a_log, d_skip, arena, (T*)y, cu_q, state_slots, sh);
+    return launch_status();
+}
+
+template <typename T>
+int dispatch_scan_prompt(const void* x, const void* xz, const void* bc, long bc_tok, const float* dt_pre, const float* dt_bias,
+                         const float* a_log, const float* d_skip, float* arena, void* y, const int* cu_q, const int* state_slots,
+                         int n_seqs, const ScanShape& sh, cudaStream_t stream) {
+#define PB_SCAN(G, SPL) return launch_scan_prompt<T, G, SPL>(x, xz, bc, bc_tok, dt_pre, dt_bias, a_log, d_skip, arena, y, cu_q, state_slots, n_seqs, sh, stream)
+    const int S = sh.n_state;
+    if (S <= 8) PB_SCAN(8, 1);
+    if (S <= 16) PB_SCAN(8, 2);
+    if (S <= 32) PB_SCAN(8, 4);
+    if (S <= 64) PB_SCAN(8, 8);
+    if (S <= 128) PB_SCAN(32, 4);
+    PB_SCAN(32, 8);
+#undef PB_SCAN
+}
+
 template <typename T, int G>
 int launch_scan(const void* x, const void* xz, const void* proj, const void* w_dt, const float* dt_bias, const float* a_log,
                 const float* d_skip, float* arena, void* y, const int* cu_q, const int* state_slots, int n_seqs,
@@ -223,5 +358,25 @@ PB_EXPORT int pb_selective_scan(int dtype, const void* x, const void* xz, long x
     if (dtype == PB_BF16)
         return dispatch_scan<__nv_bfloat16>(x, xz, proj, w_dt, dt_bias, a_log, d_skip, arena, y, cu_q, state_slots, n_seqs, sh,
                                             stream);
+    return PB_ERR_BAD_DTYPE;
+}
+
+// The same scan with the step sizes' product done beforehand: dt_pre [N, inner] float32 = W_dt r (no bias yet), and
+// bc [N, bc_tok] whose rows start with [B: state | C: state].  For steps with prompt portions.
+PB_EXPORT int pb_selective_scan_prompt(int dtype, const void* x, const void* xz, long xz_tok, const void* bc, long bc_tok,
+                                       const float* dt_pre, const float* dt_bias, const float* a_log, const float* d_skip,
+                                       float* arena, long slot_stride, long tail_offset, void* y, const int* cu_q,
+                                       const int* state_slots, int n_seqs, int inner, int n_state, int n_taps, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (inner <= 0 || n_state <= 0 || n_taps < 1) return PB_ERR_BAD_SIZE;
+    if (n_state > 32 * kStatesPerLane) return PB_ERR_TOO_LARGE;
+    if ((size_t)kStage * (2 * n_state + 3 * 16) * sizeof(float) > 48 * 1024) return PB_ERR_TOO_LARGE;
+    const ScanShape sh{inner, n_state, 0, n_taps, slot_stride, tail_offset, xz_tok, 0};
+    if (dtype == PB_F32)
+        return dispatch_scan_prompt<float>(x, xz, bc, bc_tok, dt_pre, dt_bias, a_log, d_skip, arena, y, cu_q, state_slots, n_seqs, sh,
+                                           stream);
+    if (dtype == PB_BF16)
+        return dispatch_scan_prompt<__nv_bfloat16>(x, xz, bc, bc_tok, dt_pre, dt_bias, a_log, d_skip, arena, y, cu_q, state_slots,
+                                                   n_seqs, sh, stream);
     return PB_ERR_BAD_DTYPE;
 }

@@ -11,6 +11,8 @@ from ..config.registry import MIXERS
 from ..config.specs import MixerSpec
 from .base import CacheView, Mixer, StepContext, WeightSpec
 
+PROMPT_MIN_TOKENS = 16      # steps of more tokens take the scan kernel for portions
+
 
 @MIXERS.register("selective_scan")
 class SelectiveScan(Mixer):
@@ -60,6 +62,9 @@ class SelectiveScan(Mixer):
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.w = {role: tensors[self.prefix + n] for role, n in self.names.items()}
+        # the two parts of the input-dependent projection as products of their own (steps with prompt portions)
+        self.w_x_r = self.w["x"][:self.dt_rank].contiguous()
+        self.w_x_bc = self.w["x"][self.dt_rank:].contiguous()
 
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.w.values())
@@ -73,10 +78,23 @@ class SelectiveScan(Mixer):
         ops.linear(h, w["in"], xz)
         x = ctx.scratch("scan.x", (n, self.inner))
         ops.causal_conv_silu(ctx, xz, self.inner, w["conv"], w["conv_bias"], cache.state, self.tail_offset, x)
-        proj = ctx.scratch("scan.proj", (n, self.dt_rank + 2 * self.n_state))
-        ops.linear(x, w["x"], proj)
         y = ctx.scratch("scan.y", (n, self.inner))
-        ops.selective_scan(ctx, x, xz, proj, w["dt"], w["dt_bias"], w["a_log"], w["d"], cache.state, self.tail_offset, self.taps, y)
+        if n > PROMPT_MIN_TOKENS:
+            # many tokens: the step sizes' product runs as a product (float32 out), and the scan kernel for portions takes
+            # four tokens at a time (a function of the step's size alone; a captured step of single tokens never comes here)
+            r = ctx.scratch("scan.r", (n, self.dt_rank))
+            ops.linear(x, self.w_x_r, r)
+            bc = ctx.scratch("scan.bc", (n, 2 * self.n_state))
+            ops.linear(x, self.w_x_bc, bc)
+            dt_pre = ctx.scratch("scan.dt", (n, self.inner), torch.float32)
+            ops.linear(r, w["dt"], dt_pre)
+            ops.selective_scan_prompt(ctx, x, xz, bc, dt_pre, w["dt_bias"], w["a_log"], w["d"], cache.state, self.tail_offset,
+                                      self.taps, y)
+        else:
+            proj = ctx.scratch("scan.proj", (n, self.dt_rank + 2 * self.n_state))
+            ops.linear(x, w["x"], proj)
+            ops.selective_scan(ctx, x, xz, proj, w["dt"], w["dt_bias"], w["a_log"], w["d"], cache.state, self.tail_offset,
+                               self.taps, y)
         out = ctx.scratch("scan.out", (n, self.spec.hidden))
         ops.linear(y, w["o"], out)
         return out
