@@ -22,7 +22,7 @@
 //
 // Also here: the kernel that splits a fused projection row [q | k | v] of such widths into float32
 // queries and the pages.
-#include "common.cuh"
+#include "mma_common.cuh"
 
 namespace {
 
@@ -205,7 +205,6 @@ struct TiledShape {
     int v_in_k;
 };
 
-template <typename T> __device__ __forceinline__ void zero16(T* p) { *reinterpret_cast<uint4*>(p) = make_uint4(0, 0, 0, 0); }
 
 template <typename T, int ACC>
 __global__ void __launch_bounds__(128)
@@ -217,7 +216,7 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
     const GeneralShape& sh = ts.g;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int Dk = sh.Dk, Dv = sh.Dv, GH = sh.Hq / sh.Hkv;
-    float* q_s = reinterpret_cast<float*>(smem_raw);                         // [kRows][Dk], times scale
+    float* q_s = reinterpret_cast<float*>(smem_raw);                         // [kRows][Dk]
     float* p_s = q_s + kRows * Dk;                                            // [kRows][kTile]
     T* k_s = reinterpret_cast<T*>(p_s + kRows * kTile);                       // [kTile][k_row]
     T* v_s = ts.v_in_k ? k_s : k_s + (size_t)kTile * ts.k_row;                // [kTile][v_row]
@@ -269,14 +268,17 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
         lo_r[r] = lo;
         slope[r] = slopes ? slopes[head[r]] : 0.0f;
     }
-    for (int i = threadIdx.x; i < kRows * Dk; i += blockDim.x) {
-        const int row = i / Dk, d = i % Dk;
-        float v = 0.0f;
-        if (row < n_rows) {
-            const int idx = idx0 + row;
-            v = q[((size_t)(q0 + idx / GH) * sh.Hq + g * GH + idx % GH) * Dk + d] * sh.scale;
+    // the rows' queries, 16 bytes at a time, all copies in flight at once (the scale enters with the scores)
+    {
+        const int q_chunks = Dk / 4;
+        for (int c = threadIdx.x; c < kRows * q_chunks; c += blockDim.x) {
+            const int row = c / q_chunks, part = c % q_chunks;
+            const bool on = row < n_rows;
+            const int idx = idx0 + (on ? row : 0);
+            const float* src = q + ((size_t)(q0 + idx / GH) * sh.Hq + g * GH + idx % GH) * Dk + part * 4;
+            cp_async16(smem_u32(q_s + (size_t)row * Dk + part * 4), src, on);
         }
-        q_s[i] = v;
+        cp_async_commit();
     }
 
     float m_run[4], l_run[4], acc[4][ACC];
@@ -291,28 +293,28 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
     const int k_chunks = Dk / V, v_chunks = Dv / V;
     for (int kt = t_begin; kt < t_end; ++kt) {
         const int j0 = kt * kTile;
-        __syncthreads();                                   // the tile before is done with (and q_s is written)
-        for (int c = threadIdx.x; c < kTile * k_chunks; c += blockDim.x) {
-            const int key = c / k_chunks, part = c % k_chunks;
+        __syncthreads();                                   // the tile before is done with
+        {
+            // four threads per key: one look into the block table, then the row's 16-byte pieces, all in flight at once
+            const int key = threadIdx.x >> 2, sub = threadIdx.x & 3;
             const int j = j0 + key;
-            T* dst = k_s + (size_t)key * ts.k_row + part * V;
-            if (j < lo_blk || j > hi_blk) { zero16(dst); continue; }
-            int page = table[j / sh.page_size];
-            if (!page_ok(page, bounds)) page = 0;
-            const T* src = k_pool + (((size_t)page * sh.Hkv + g) * sh.page_size + j % sh.page_size) * sh.k_stride + part * V;
-            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-        }
-        if (!ts.v_in_k) {
-            for (int c = threadIdx.x; c < kTile * v_chunks; c += blockDim.x) {
-                const int key = c / v_chunks, part = c % v_chunks;
-                const int j = j0 + key;
-                T* dst = v_s + (size_t)key * ts.v_row + part * V;
-                if (j < lo_blk || j > hi_blk) { zero16(dst); continue; }
+            const bool ok = j >= lo_blk && j <= hi_blk;        // rows outside the block's span are filled with zeros
+            const T* k_src = k_pool;
+            const T* v_src = v_pool;
+            if (ok) {
                 int page = table[j / sh.page_size];
                 if (!page_ok(page, bounds)) page = 0;
-                const T* src = v_pool + (((size_t)page * sh.Hkv + g) * sh.page_size + j % sh.page_size) * sh.v_stride + part * V;
-                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+                const size_t at = ((size_t)page * sh.Hkv + g) * sh.page_size + j % sh.page_size;
+                k_src = k_pool + at * sh.k_stride;
+                v_src = v_pool + at * sh.v_stride;
             }
+            for (int part = sub; part < k_chunks; part += 4)
+                cp_async16(smem_u32(k_s + (size_t)key * ts.k_row + part * V), k_src + part * V, ok);
+            if (!ts.v_in_k)
+                for (int part = sub; part < v_chunks; part += 4)
+                    cp_async16(smem_u32(v_s + (size_t)key * ts.v_row + part * V), v_src + part * V, ok);
+            cp_async_commit();
+            cp_async_wait<0>();
         }
         __syncthreads();
 
@@ -339,7 +341,7 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             const bool vis = j >= lo_r[r] && j <= pos[r];
-            const float v = vis ? sc[r] - slope[r] * (float)(pos[r] - j) : -INFINITY;
+            const float v = vis ? fmaf(sc[r], sh.scale, -slope[r] * (float)(pos[r] - j)) : -INFINITY;
             const float m_new = fmaxf(m_run[r], warp_max(v));
             float pv = 0.0f, corr = 1.0f;
             if (m_new != -INFINITY) {                       // uniform over the warp
@@ -380,6 +382,7 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
         __syncwarp();
     }
 
+    cp_async_wait<0>();                                    // a block without tiles still has its queries on their way
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
         if (warp * 4 + r >= n_rows) continue;
@@ -568,7 +571,8 @@ PB_EXPORT int pb_paged_attention_general_tiled(int dtype, const float* q, const 
                                                int page_size, float scale, int window, int chunk, cudaStream_t stream) {
     if (n_tokens <= 0 || row_tiles <= 0) return 0;
     if (!pb_attention_general_tiled_supported(dtype, k_pool, v_pool, Hq, Hkv, Dk, Dv, k_stride, v_stride)) return PB_ERR_BAD_SIZE;
-    if (page_size <= 0 || window < 0 || chunk < 0 || n_splits < 1 || n_splits > 65535 || (n_splits > 1 && partial == nullptr))
+    if (page_size <= 0 || window < 0 || chunk < 0 || n_splits < 1 || n_splits > 65535 || (n_splits > 1 && partial == nullptr) ||
+        (uintptr_t)q % 16)
         return PB_ERR_BAD_SIZE;
     if (Hkv > 65535) return PB_ERR_TOO_LARGE;
     TiledShape ts{};
