@@ -89,6 +89,24 @@ __device__ __forceinline__ bool slot_ok(int slot, int page_size, const PoolBound
     return true;
 }
 
+// The gating of a fused gate/up product, carried with the product's `inter` (the output's width) so that it reaches every
+// epilogue: out = g' * sigmoid(alpha * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit).  SwiGLU is
+// limit = inf, alpha = 1, shift = 0 (the formula then is silu(g) * u to the last bit); a clamped gated unit gives its own.
+// The host sets what the next gated launches use (pb_set_gating) and the launchers read it with gating_now(inter).
+struct GatedInter {
+    int n;
+    float limit, alpha, shift;
+    __host__ __device__ GatedInter(int n_ = 0, float limit_ = __builtin_huge_valf(), float alpha_ = 1.0f, float shift_ = 0.0f)
+        : n(n_), limit(limit_), alpha(alpha_), shift(shift_) {}
+    __host__ __device__ operator int() const { return n; }
+};
+GatedInter gating_now(int inter);        // host side: `inter` with the gating that pb_set_gating set last
+__device__ __forceinline__ float gated(float g, float u, const GatedInter& p) {
+    g = fminf(g, p.limit);
+    u = fminf(fmaxf(u, -p.limit), p.limit);
+    return g / (1.0f + expf(-p.alpha * g)) * (u + p.shift);
+}
+
 // Programmatic dependent launch.  A kernel launched through launch_pdl may be brought onto the
 // SMs while the kernel before it on the stream is finishing: as soon as every block of that
 // kernel has called pdl_trigger (or exited).  It must call pdl_wait before it touches anything

@@ -407,6 +407,17 @@ static PoolBounds g_pool_bounds = {0, nullptr};
 PoolBounds pool_bounds_now() { return g_pool_bounds; }
 }  // namespace pb
 
+namespace pb {
+static GatedInter g_gating;
+GatedInter gating_now(int inter) { GatedInter g = g_gating; g.n = inter; return g; }
+}  // namespace pb
+
+// The gating that fused gate/up products launched from now on apply (see GatedInter in common.cuh); limit <= 0 sets
+// SwiGLU (no clamp, alpha 1, shift 0).
+PB_EXPORT void pb_set_gating(float limit, float alpha, float shift) {
+    pb::g_gating = limit > 0.0f ? pb::GatedInter(0, limit, alpha, shift) : pb::GatedInter();
+}
+
 // 1 in a build with the bounds checks (see common.cuh), else 0.
 PB_EXPORT int pb_bounds_checked(void) {
 #ifdef PB_CHECK_BOUNDS

@@ -47,7 +47,7 @@ enum { kPlain = 0, kSwiGLU = 1 };
 template <int NT, int MODE, typename OutT, int kUnroll>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
-                   int inter) {
+                   const GatedInter inter) {
     __shared__ float red[kWarps][kRows][8 * NT + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -134,7 +134,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT*
             float gate = 0.0f, up = 0.0f;
 #pragma unroll
             for (int wi = 0; wi < kWarps; ++wi) { gate += red[wi][r][token]; up += red[wi][r + 8][token]; }
-            out[(size_t)token * inter + blockIdx.x * 8 + r] = from_float<OutT>(gate / (1.0f + expf(-gate)) * up);
+            out[(size_t)token * inter + blockIdx.x * 8 + r] = from_float<OutT>(gated(gate, up, inter));
         }
     } else {
         for (int i = tid; i < kRows * M; i += kWarps * 32) {
@@ -235,7 +235,7 @@ struct SkinnyFuse {
 template <int NT, int MODE, typename OutT, int kUnroll, bool kEvictFirst, int kPre, bool kScaled = false, bool kAcc = false>
 __device__ __forceinline__ void
 skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
-                 int inter, const SkinnyFuse fuse = SkinnyFuse{}) {
+                 const GatedInter inter, const SkinnyFuse fuse = SkinnyFuse{}) {
     constexpr int kWideK = 64;                        // k per load: 4 threads x 16 contiguous elements
     constexpr int kPreRow = kPre * 128 + 16;          // bytes of a row's prefetched part in shared memory
     __shared__ float red[kWarps][kRows][8 * NT + 1];
@@ -410,7 +410,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
 #pragma unroll
             for (int wi = 0; wi < kWarps; ++wi) { gate += red[wi][r][token]; up += red[wi][r + 8][token]; }
             if constexpr (kScaled) { gate *= scale_s[token]; up *= scale_s[token]; }
-            out[(size_t)token * inter + bid * 8 + r] = from_float<OutT>(gate / (1.0f + expf(-gate)) * up);
+            out[(size_t)token * inter + bid * 8 + r] = from_float<OutT>(gated(gate, up, inter));
         }
     } else {
         static_assert(kRows * 8 * NT <= kWarps * 32, "one output per thread");
@@ -450,7 +450,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
 template <int NT, int MODE, typename OutT, int kUnroll, bool kEvictFirst>
 __global__ void __launch_bounds__(kWarps * 32, kUnroll <= 2 ? 3 : 2)
 gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
-                        int inter) {
+                        const GatedInter inter) {
     skinny_wide_body<NT, MODE, OutT, kUnroll, kEvictFirst, 0>(x, w, out, M, N, K, inter);
 }
 
@@ -459,7 +459,7 @@ gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, 
 template <int NT, int MODE, typename OutT, int kUnroll>
 __global__ void __launch_bounds__(kWarps * 32, kUnroll <= 2 ? 3 : 2)
 gemm_skinny_wide_prefetch_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N,
-                                 int K, int inter) {
+                                 int K, const GatedInter inter) {
     skinny_wide_body<NT, MODE, OutT, kUnroll, true, 2>(x, w, out, M, N, K, inter);
 }
 
@@ -467,7 +467,7 @@ gemm_skinny_wide_prefetch_kernel(const bf16* __restrict__ x, const bf16* __restr
 template <int NT, int MODE, int kUnroll, int kPre>
 __global__ void __launch_bounds__(kWarps * 32, kUnroll <= 2 ? 3 : 2)
 gemm_skinny_scaled_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w, bf16* __restrict__ out, int M, int N, int K,
-                          int inter, const SkinnyFuse fuse) {
+                          const GatedInter inter, const SkinnyFuse fuse) {
     skinny_wide_body<NT, MODE, bf16, kUnroll, true, kPre, true, false>(y, w, out, M, N, K, inter, fuse);
 }
 
@@ -488,7 +488,7 @@ gemm_skinny_accumulate_kernel(const bf16* __restrict__ x, const bf16* __restrict
 constexpr int kTallGroups = 2;
 template <int MODE, typename OutT>
 __global__ void __launch_bounds__(kWarps * 32, 2)
-gemm_skinny_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K, int inter) {
+gemm_skinny_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K, const GatedInter inter) {
     constexpr int NT = 2, kU = 2, kWideK = 64;
     __shared__ float red[kWarps][kTallGroups * kRows][8 * NT + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -585,7 +585,7 @@ gemm_skinny_tall_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, 
             float gate = 0.0f, up = 0.0f;
 #pragma unroll
             for (int wi = 0; wi < kWarps; ++wi) { gate += red[wi][row][token]; up += red[wi][row + 8][token]; }
-            out[(size_t)token * inter + blockIdx.x * 16 + j] = from_float<OutT>(gate / (1.0f + expf(-gate)) * up);
+            out[(size_t)token * inter + blockIdx.x * 16 + j] = from_float<OutT>(gated(gate, up, inter));
         }
     } else {
         for (int i = tid; i < kTallGroups * kRows * M; i += kWarps * 32) {
@@ -629,7 +629,7 @@ bool prefetch_enabled() {          // PULSAR_SKINNY_PREFETCH=0: no part of the w
 template <int NT, int kU, bool kEvictFirst>
 int launch_wide(int mode, int out_dtype, const bf16* xp, const bf16* wp, void* out, int M, int N, int K, cudaStream_t stream) {
     if (mode == kSwiGLU) {
-        const int inter = N / 2;
+        const GatedInter inter = gating_now(N / 2);
         if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
         return launch_pdl(gemm_skinny_wide_kernel<NT, kSwiGLU, bf16, kU, kEvictFirst>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
     }
@@ -641,7 +641,7 @@ int launch_wide(int mode, int out_dtype, const bf16* xp, const bf16* wp, void* o
 template <int NT, int kU>
 int launch_prefetch(int mode, int out_dtype, const bf16* xp, const bf16* wp, void* out, int M, int N, int K, cudaStream_t stream) {
     if (mode == kSwiGLU) {
-        const int inter = N / 2;
+        const GatedInter inter = gating_now(N / 2);
         if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
         return launch_pdl(gemm_skinny_wide_prefetch_kernel<NT, kSwiGLU, bf16, kU>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
     }
@@ -661,7 +661,7 @@ int launch_u(int mode, int out_dtype, const void* x, const void* w, void* out, i
         return launch_wide<NT, kU, true>(mode, out_dtype, xp, wp, out, M, N, K, stream);
     }
     if (mode == kSwiGLU) {
-        const int inter = N / 2;
+        const GatedInter inter = gating_now(N / 2);
         if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
         return launch_pdl(gemm_skinny_kernel<NT, kSwiGLU, bf16, kUnroll>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
     }
@@ -773,7 +773,7 @@ PB_EXPORT int pb_gemm_skinny_scaled(int mode, const void* y, const void* w, void
     fuse.publish = g_publish_sums;
     fuse.eps = eps;
     const int tiles = (mode == kSwiGLU) ? N / 2 / 8 : N / kRows;
-    const int inter = mode == kSwiGLU ? N / 2 : 0;
+    const GatedInter inter = gating_now(mode == kSwiGLU ? N / 2 : 0);
     const bool many = tiles > 2 * sm_count();
 #define PB_SCALED(NT, MODE, KU, PRE) \
     return launch_pdl(gemm_skinny_scaled_kernel<NT, MODE, KU, PRE>, tiles + 1, kWarps * 32, 0, stream, yp, wp, (bf16*)out, M, N, K, inter, fuse)

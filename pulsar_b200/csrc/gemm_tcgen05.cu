@@ -142,7 +142,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {               /
 template <int MODE, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         OutT* __restrict__ out, int M, int N, int K, int inter, int m_tiles, int n_tiles) {
+                         OutT* __restrict__ out, int M, int N, int K, const GatedInter inter, int m_tiles, int n_tiles) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);   // full, empty, acc_full, acc_empty
@@ -252,7 +252,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const float g = __uint_as_float(gv[i]), u = __uint_as_float(uv[i]);
-                        f[i] = g / (1.0f + expf(-g)) * u;
+                        f[i] = gated(g, u, inter);
                     }
                     if (row < M && n0 + c < inter) store32(out + (size_t)row * inter + n0 + c, f, inter - (n0 + c));
                 }
@@ -288,7 +288,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 template <int MODE, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    OutT* __restrict__ out, int M, int N, int K, int inter, int m_tiles, int n_tiles) {
+                    OutT* __restrict__ out, int M, int N, int K, const GatedInter inter, int m_tiles, int n_tiles) {
     extern __shared__ unsigned char smem_raw[];
     // 128-byte swizzled tiles want 1024-byte alignment.
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -332,7 +332,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     mbar_expect_tx(full0 + 8 * s, kStageBytes);
                     tma_load_2d(a_dst, &map_x, full0 + 8 * s, kt * kBK, m0);
                     tma_load_2d(b_dst, &map_w, full0 + 8 * s, kt * kBK, n0);
-                    tma_load_2d(b_dst + kBBytes / 2, &map_w, full0 + 8 * s, kt * kBK, (MODE == kSwiGLU ? inter : kBN / 2) + n0);
+                    tma_load_2d(b_dst + kBBytes / 2, &map_w, full0 + 8 * s, kt * kBK, (MODE == kSwiGLU ? (int)inter : kBN / 2) + n0);
                 }
                 if (!ok) { *abort_flag = 1; atomicMax(&g_tc5_error, 2u); break; }
             }
@@ -391,7 +391,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const float g = __uint_as_float(gv[i]), u = __uint_as_float(uv[i]);
-                        f[i] = g / (1.0f + expf(-g)) * u;
+                        f[i] = gated(g, u, inter);
                     }
                     if (row < M && n0 + c < inter) store32(out + (size_t)row * inter + n0 + c, f, inter - (n0 + c));
                 }
@@ -454,7 +454,7 @@ int sm_count() {
 }
 
 template <int MODE, typename OutT>
-int launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int inter, int m_tiles, int n_tiles,
+int launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, const GatedInter inter, int m_tiles, int n_tiles,
            cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
@@ -557,7 +557,7 @@ PB_EXPORT int pb_gemm_tcgen05(int mode, int out_dtype, const void* x, const void
     const int m_tiles = (M + kBM - 1) / kBM;
     if (mode == kSwiGLU) {
         if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
-        const int inter = N / 2;
+        const GatedInter inter = gating_now(N / 2);
         return launch<kSwiGLU, bf16>(mx, mw, out, M, N, K, inter, m_tiles, (inter + kBN / 2 - 1) / (kBN / 2), stream);
     }
     const int n_tiles = (N + kBN - 1) / kBN;

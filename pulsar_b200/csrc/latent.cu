@@ -69,13 +69,14 @@ heads_linear_wide_kernel(const T* __restrict__ a, long a_tok, int a_head, const 
 }
 
 constexpr int kSlices = 4;      // a block's 128 threads: 32 outputs x 4 slices of K
+constexpr int kBatch = 16;      // weights a thread asks for before it uses the first
 
 template <typename T, typename TO>
 __global__ void __launch_bounds__(128)
 heads_linear_kernel(const T* __restrict__ a, long a_tok, int a_head, const T* __restrict__ w, TO* __restrict__ out, long o_tok,
                     int o_head, const T* __restrict__ gate, long g_tok, int N, int M, int K) {
     extern __shared__ __align__(16) float smem[];
-    const int KS = (((K + kSlices - 1) / kSlices) + 3) & ~3;      // k's per slice, a multiple of 4
+    const int KS = (((K + kSlices - 1) / kSlices) + kBatch - 1) / kBatch * kBatch;      // k's per slice, a multiple of kBatch
     const int KP = KS * kSlices;
     float* a_s = smem;                             // [kTok][KP], zeros behind K
     float* r_s = a_s + kTok * KP;                  // [kSlices][kTok][32] partial sums
@@ -94,17 +95,20 @@ heads_linear_kernel(const T* __restrict__ a, long a_tok, int a_head, const T* __
 #pragma unroll
     for (int tt = 0; tt < kTok; ++tt) acc[tt] = 0.0f;
     const int k0 = slice * KS;
-    for (int k = k0; k < k0 + KS; k += 4) {
-        float wv[4];
+    for (int k = k0; k < k0 + KS; k += kBatch) {
+        float wv[kBatch];                          // a batch of weights on their way at once
 #pragma unroll
-        for (int e = 0; e < 4; ++e) wv[e] = (live && k + e < K) ? to_float(wh[(size_t)(k + e) * M]) : 0.0f;
+        for (int e = 0; e < kBatch; ++e) wv[e] = (live && k + e < K) ? to_float(wh[(size_t)(k + e) * M]) : 0.0f;
 #pragma unroll
-        for (int tt = 0; tt < kTok; ++tt) {
-            const float4 av = *reinterpret_cast<const float4*>(a_s + tt * KP + k);
-            acc[tt] = fmaf(av.x, wv[0], acc[tt]);
-            acc[tt] = fmaf(av.y, wv[1], acc[tt]);
-            acc[tt] = fmaf(av.z, wv[2], acc[tt]);
-            acc[tt] = fmaf(av.w, wv[3], acc[tt]);
+        for (int e = 0; e < kBatch; e += 4) {
+#pragma unroll
+            for (int tt = 0; tt < kTok; ++tt) {
+                const float4 av = *reinterpret_cast<const float4*>(a_s + tt * KP + k + e);
+                acc[tt] = fmaf(av.x, wv[e], acc[tt]);
+                acc[tt] = fmaf(av.y, wv[e + 1], acc[tt]);
+                acc[tt] = fmaf(av.z, wv[e + 2], acc[tt]);
+                acc[tt] = fmaf(av.w, wv[e + 3], acc[tt]);
+            }
         }
     }
 #pragma unroll
@@ -221,7 +225,7 @@ int launch_heads(const void* a, long a_tok, int a_head, const void* w, void* out
             (const T*)a, a_tok, a_head, (const T*)w, (TO*)out, o_tok, o_head, (const T*)gate, g_tok, N, M, K);
         return launch_status();
     }
-    const int ks = (((K + kSlices - 1) / kSlices) + 3) & ~3;
+    const int ks = (((K + kSlices - 1) / kSlices) + kBatch - 1) / kBatch * kBatch;
     dim3 grid((N + kTok - 1) / kTok, H, (M + 31) / 32);
     heads_linear_kernel<T, TO><<<grid, 128, sizeof(float) * kTok * (ks * kSlices + kSlices * 32), stream>>>((const T*)a, a_tok, a_head, (const T*)w, (TO*)out,
                                                                                  o_tok, o_head, (const T*)gate, g_tok, N, M, K);

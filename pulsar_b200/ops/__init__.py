@@ -79,6 +79,7 @@ _SIGNATURES = {
     "pb_gather_words": [_P, _I, _P, _P],
     "pb_bounds_checked": [],
     "pb_set_pool_bounds": [_I, _P],
+    "pb_set_gating": [_F, _F, _F],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P],
     "pb_sample_workspace": [_I],
@@ -312,10 +313,27 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
                           _p(work), _p(keys), _p(out), stream()), "sample", kernels=(2 if any_greedy else 0) + (5 if filtered else 2))
 
 
-def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> bool:
+class _Gating:
+    """The gating of the fused gate/up products launched inside: (limit, alpha, shift) for
+    out = g' * sigmoid(alpha * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit); None: SwiGLU."""
+
+    def __init__(self, gating):
+        self.gating = gating
+
+    def __enter__(self):
+        if self.gating is not None:
+            fn("pb_set_gating")(float(self.gating[0]), float(self.gating[1]), float(self.gating[2]))
+
+    def __exit__(self, *exc):
+        if self.gating is not None:
+            fn("pb_set_gating")(0.0, 1.0, 0.0)
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False, gating=None) -> bool:
     """The weight-streaming product for up to 16 tokens (bfloat16).  ``swiglu``: ``w`` holds
-    gate rows then up rows and ``out`` [M, inter] receives silu(gate) * up.  Returns False,
-    having done nothing, when the sizes are not the kernel's."""
+    gate rows then up rows and ``out`` [M, inter] receives silu(gate) * up, or with ``gating`` =
+    (limit, alpha, shift) the clamped form min(gate, limit) * sigmoid(alpha * .) * (clamp(up) + shift).
+    Returns False, having done nothing, when the sizes are not the kernel's."""
     m, k = a.shape
     n = w.shape[0]
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k:
@@ -325,7 +343,8 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: boo
         return False
     _cuda(a, w, out)
     assert out.shape == (m, n // 2 if swiglu else n)
-    check(fn("pb_gemm_skinny")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream()), "gemm_skinny")
+    with _Gating(gating if swiglu else None):
+        check(fn("pb_gemm_skinny")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream()), "gemm_skinny")
     return True
 
 
@@ -399,7 +418,7 @@ def linear_prenormed(prepared: torch.Tensor, parts: torch.Tensor, eps: float, w:
     return True
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> bool:
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False, gating=None) -> bool:
     """The tcgen05 / TMA product for many tokens (bfloat16 operands, float32 accumulation in
     tensor memory).  ``swiglu`` as in ``gemm_skinny``.  Returns False, having done nothing,
     when the sizes are not the kernel's (K must be a multiple of 8)."""
@@ -412,7 +431,8 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bo
         return False
     _cuda(a, w, out)
     assert out.shape == (m, n // 2 if swiglu else n)
-    check(fn("pb_gemm_tcgen05")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream()), "gemm_tcgen05")
+    with _Gating(gating if swiglu else None):
+        check(fn("pb_gemm_tcgen05")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream()), "gemm_tcgen05")
     return True
 
 
@@ -627,23 +647,29 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
             out.copy_(torch.mm(a, w.t(), out_dtype=torch.float32))
 
 
-def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out [M, I] = silu(a Wg^T) * (a Wu^T) with ``w_gate_up`` = gate rows then up rows.  In
-    bfloat16, up to 16 rows (the weight-streaming kernel) and more than 128 rows (the tcgen05 kernel)
+def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, gating=None) -> None:
+    """out [M, I] = silu(a Wg^T) * (a Wu^T) with ``w_gate_up`` = gate rows then up rows; with ``gating`` = (limit, alpha,
+    shift) the clamped form g * sigmoid(alpha * g) * (u + shift), g = min(a Wg^T, limit), u = clamp(a Wu^T, -limit, limit).
+    In bfloat16, up to 16 rows (the weight-streaming kernel) and more than 128 rows (the tcgen05 kernel)
     take one kernel that never writes the [M, 2I] intermediate; otherwise the product followed by the
     gating kernel."""
-    if gemm_skinny(a, w_gate_up, out, swiglu=True):
+    if gemm_skinny(a, w_gate_up, out, swiglu=True, gating=gating):
         return
-    if _stream_wanted(a.shape[0], w_gate_up.shape[0]) and gemm_tcgen05_stream(a, w_gate_up, out, swiglu=True):
+    if gating is None and _stream_wanted(a.shape[0], w_gate_up.shape[0]) and gemm_tcgen05_stream(a, w_gate_up, out, swiglu=True):
         return
     # Between 17 and 128 rows the product is still bound by streaming the weights, which the library's small
     # tiles do faster (4.5 against 3.2 TB/s at the 8B sizes) than the tcgen05 kernel's 128 x 256 tiles.
     fused = GEMM_BACKEND == "tcgen05" or (GEMM_BACKEND == "auto" and a.shape[0] > 128)
-    if fused and gemm_tcgen05(a, w_gate_up, out, swiglu=True):
+    if fused and gemm_tcgen05(a, w_gate_up, out, swiglu=True, gating=gating):
         return
     gate_up = ctx.scratch("mlp.gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
     linear(a, w_gate_up, gate_up)
-    silu_mul(gate_up, out)
+    if gating is None:
+        silu_mul(gate_up, out)
+    else:
+        if gating[2] != 1.0:
+            raise KernelError("gated_linear: the gating kernel of the unfused path adds 1 to the clamped up part")
+        clamped_glu(gate_up, out, gating[0], gating[1])
 
 
 _FORCED_SPLITS = int(os.environ.get("PULSAR_DECODE_SPLITS", "0") or 0)      # > 0: this many splits, for measurements

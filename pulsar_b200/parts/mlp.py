@@ -95,10 +95,8 @@ class ClampedGLU(FeedForward):
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         s, n = self.spec, ctx.n_tokens
-        gate_up = ctx.scratch("mlp.gate_up", (n, 2 * s.intermediate))
-        ops.linear(h, self.w_gate_up, gate_up)
         act = ctx.scratch("mlp.act", (n, s.intermediate))
-        ops.clamped_glu(gate_up, act, self.limit, self.alpha)
+        ops.gated_linear(ctx, h, self.w_gate_up, act, gating=(self.limit, self.alpha, 1.0))     # the gating in the product's epilogue where it fuses
         out = ctx.scratch("mlp.out", (n, s.hidden))
         ops.linear(act, self.w_down, out)
         return out

@@ -443,6 +443,29 @@ def test_small_kernels_against_their_formulas(dtype):
 
 
 @gpu
+@pytest.mark.parametrize("rows", [1, 8, 16, 40, 200])
+def test_clamped_gating_inside_the_gate_up_product(rows):
+    """The gate/up product with the clamped gating in its epilogue (the weight-streaming kernel up to 16 rows, the tcgen05
+    kernel above 128) and the unfused path between them, against the formula; SwiGLU through the same kernels is unchanged."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(rows)
+    width, inter = 128, 192
+    a = torch.randn(rows, width, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, width, generator=g) * 0.3).to(torch.bfloat16)
+    ctx = types.SimpleNamespace(scratch=lambda tag, shape, dtype=None: torch.empty(shape, dtype=dtype, device="cuda"))
+    gu = a.double() @ w.double().T
+    gate, up = gu[:, :inter], gu[:, inter:]
+    out = torch.empty(rows, inter, dtype=torch.bfloat16, device="cuda")
+    ops.gated_linear(ctx, a.cuda(), w.cuda(), out, gating=(1.5, 1.702, 1.0))
+    gg, uu = gate.clamp(max=1.5), up.clamp(-1.5, 1.5)
+    want = gg * torch.sigmoid(1.702 * gg) * (uu + 1)
+    assert float((out.double().cpu() - want).abs().max() / want.abs().max()) < 1e-2
+    ops.gated_linear(ctx, a.cuda(), w.cuda(), out)
+    want = gate * torch.sigmoid(gate) * up
+    assert float((out.double().cpu() - want).abs().max() / want.abs().max()) < 1e-2
+
+
+@gpu
 def test_scan_kernels_carry_their_state_across_portions():
     """Convolution and scan over two sequences whose tokens arrive in portions of 1 to 7, against the whole sequences
     in one go; the second sequence's slot was used before and zeroed."""
