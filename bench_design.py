@@ -158,6 +158,13 @@ def own_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
         "clamped_glu": (g * 3 * n * z["ff"] * 6, 0.0, ""),
     }
     work["paged_attention_general_tiled"] = work["paged_attention_general"]          # the same job, by the other kernel
+    # a step of whole prompts: latent attention in its expanded form (keys dim + rot wide, values dim wide, a head of its own
+    # each) and the chunked attention, on the tensor cores (useful operations; the kernel issues two MMAs for each)
+    work["paged_attention_general_tc"] = (g * (2 * n * H * ((d + rot) * (4 + 2) + d * 4) + n * H * d * 6 + n * G * 2 * d * 2),
+                                          g * (2 * 2.0 * H * (2 * d + rot) * lat_pairs + 2.0 * H * 2 * d * att_pairs), "bf16 tensor")
+    work["selective_scan_prompt"] = (work["selective_scan"][0] + g * n * z["inner"] * 4, g * n * z["inner"] * 7.0 * z["state"], "fp32 FMA")
+    work["latent_expand_keys"] = (g * 2 * n * H * (2 * d + rot) * 2, 0.0, "")
+    work["sigmoid_gate"] = (g * 2 * n * H * d * 6, 0.0, "")
     return {k: (b * steps, f * steps, on) for k, (b, f, on) in work.items()}
 
 
