@@ -53,6 +53,8 @@ causal_conv_silu_kernel(const T* __restrict__ in, long in_tok, const float* __re
 }
 
 constexpr int kStage = 16;          // tokens staged per round
+constexpr int kStagePrompt = 32;    // the same in the kernel for portions
+constexpr int kBatchTokens = 8;     // tokens whose state-independent work that kernel does side by side
 constexpr int kStatesPerLane = 8;
 constexpr int kDtPerLane = 32;
 
@@ -164,9 +166,9 @@ selective_scan_kernel(const T* __restrict__ x, const T* __restrict__ xz, const T
 }
 
 // The scan for prompt portions: the step sizes before their bias and softplus come from a product of their own
-// (dt_pre [N, inner] float32), and the tokens of a staged round are taken four at a time: what does not depend on the
-// state (softplus, the decays' exponentials) is computed for the four first, so that only the multiply-adds of the
-// state chain from token to token, and the four sums over the state are reduced side by side.  SPL: states per lane.
+// (dt_pre [N, inner] float32), and the tokens of a staged round are taken eight at a time: what does not depend on the
+// state (softplus, the decays' exponentials) is computed for the eight first, so that only the multiply-adds of the
+// state chain from token to token, and the eight sums over the state are reduced side by side.  SPL: states per lane.
 template <typename T, int G, int SPL>
 __global__ void __launch_bounds__(128)
 selective_scan_prompt_kernel(const T* __restrict__ x, const T* __restrict__ xz, const T* __restrict__ bc, long bc_tok,
@@ -174,13 +176,13 @@ selective_scan_prompt_kernel(const T* __restrict__ x, const T* __restrict__ xz, 
                              const float* __restrict__ d_skip, float* __restrict__ arena, T* __restrict__ y,
                              const int* __restrict__ cu_q, const int* __restrict__ state_slots, const ScanShape sh) {
     constexpr int CH = 128 / G;
-    constexpr int U = 4;
+    constexpr int U = kBatchTokens;
     extern __shared__ float smem[];
     const int S = sh.n_state, inner = sh.inner;
-    float* bc_s = smem;                               // [kStage][2 * S]
-    float* x_s = bc_s + kStage * 2 * S;               // [kStage][CH]
-    float* z_s = x_s + kStage * CH;                   // [kStage][CH]
-    float* dt_s = z_s + kStage * CH;                  // [kStage][CH]
+    float* bc_s = smem;                               // [kStagePrompt][2 * S]
+    float* x_s = bc_s + kStagePrompt * 2 * S;               // [kStagePrompt][CH]
+    float* z_s = x_s + kStagePrompt * CH;                   // [kStagePrompt][CH]
+    float* dt_s = z_s + kStagePrompt * CH;                  // [kStagePrompt][CH]
 
     const int seq = blockIdx.x;
     const int group = threadIdx.x / G, gl = threadIdx.x % G;
@@ -201,14 +203,14 @@ selective_scan_prompt_kernel(const T* __restrict__ x, const T* __restrict__ xz, 
     const float bias = live ? dt_bias[c] : 0.0f;
     const float skip = live ? d_skip[c] : 0.0f;
 
-    for (int base = 0; base < q_len; base += kStage) {
-        const int nt = min(kStage, q_len - base);
+    for (int base = 0; base < q_len; base += kStagePrompt) {
+        const int nt = min(kStagePrompt, q_len - base);
         __syncthreads();
-        for (int i = threadIdx.x; i < kStage * 2 * S; i += blockDim.x) {
+        for (int i = threadIdx.x; i < kStagePrompt * 2 * S; i += blockDim.x) {
             const int tt = i / (2 * S), k = i % (2 * S);
             bc_s[i] = tt < nt ? to_float(bc[(size_t)(q0 + base + tt) * bc_tok + k]) : 0.0f;
         }
-        for (int i = threadIdx.x; i < kStage * CH; i += blockDim.x) {
+        for (int i = threadIdx.x; i < kStagePrompt * CH; i += blockDim.x) {
             const int tt = i / CH, k = i % CH;
             const bool on = tt < nt && c0 + k < inner;
             const size_t row = (size_t)(q0 + base + (on ? tt : 0));
@@ -276,7 +278,7 @@ int launch_scan_prompt(const void* x, const void* xz, const void* bc, long bc_to
                        const float* a_log, const float* d_skip, float* arena, void* y, const int* cu_q, const int* state_slots,
                        int n_seqs, const ScanShape& sh, cudaStream_t stream) {
     constexpr int CH = 128 / G;
-    const size_t smem = sizeof(float) * kStage * (2 * sh.n_state + 3 * CH);
+    const size_t smem = sizeof(float) * kStagePrompt * (2 * sh.n_state + 3 * CH);
     dim3 grid(n_seqs, (sh.inner + CH - 1) / CH);
     selective_scan_prompt_kernel<T, G, SPL><<<grid, 128, smem, stream>>>((const T*)x, (const T*)xz, (const T*)bc, bc_tok, dt_pre, dt_bias,
                                                                          a_log, d_skip, arena, (T*)y, cu_q, state_slots, sh);
@@ -361,6 +363,13 @@ PB_EXPORT int pb_selective_scan(int dtype, const void* x, const void* xz, long x
     return PB_ERR_BAD_DTYPE;
 }
 
+// 1 when the kernel for portions takes this state size (its staging fits the default shared memory), else 0: the caller
+// then uses pb_selective_scan for portions too.
+PB_EXPORT int pb_selective_scan_prompt_supported(int n_state) {
+    if (n_state <= 0 || n_state > 32 * kStatesPerLane) return 0;
+    return (size_t)kStagePrompt * (2 * n_state + 3 * 16) * sizeof(float) <= 48 * 1024 ? 1 : 0;
+}
+
 // The same scan with the step sizes' product done beforehand: dt_pre [N, inner] float32 = W_dt r (no bias yet), and
 // bc [N, bc_tok] whose rows start with [B: state | C: state].  For steps with prompt portions.
 PB_EXPORT int pb_selective_scan_prompt(int dtype, const void* x, const void* xz, long xz_tok, const void* bc, long bc_tok,
@@ -369,8 +378,7 @@ PB_EXPORT int pb_selective_scan_prompt(int dtype, const void* x, const void* xz,
                                        const int* state_slots, int n_seqs, int inner, int n_state, int n_taps, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (inner <= 0 || n_state <= 0 || n_taps < 1) return PB_ERR_BAD_SIZE;
-    if (n_state > 32 * kStatesPerLane) return PB_ERR_TOO_LARGE;
-    if ((size_t)kStage * (2 * n_state + 3 * 16) * sizeof(float) > 48 * 1024) return PB_ERR_TOO_LARGE;
+    if (!pb_selective_scan_prompt_supported(n_state)) return PB_ERR_TOO_LARGE;
     const ScanShape sh{inner, n_state, 0, n_taps, slot_stride, tail_offset, xz_tok, 0};
     if (dtype == PB_F32)
         return dispatch_scan_prompt<float>(x, xz, bc, bc_tok, dt_pre, dt_bias, a_log, d_skip, arena, y, cu_q, state_slots, n_seqs, sh,

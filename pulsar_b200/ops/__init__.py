@@ -97,6 +97,7 @@ _SIGNATURES = {
     "pb_sigmoid_gate": [_I, _P, _P, _L, _I, _I, _P],
     "pb_causal_conv_silu": [_I, _P, _L, _P, _P, _P, _L, _L, _P, _P, _P, _P, _I, _I, _I, _P],
     "pb_selective_scan": [_I, _P, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "pb_selective_scan_prompt_supported": [_I],
     "pb_selective_scan_prompt": [_I, _P, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _P],
     "pb_post_norm_add": [_I, _P, _P, _P, _F, _P, _F, _P, _I, _I, _P],
     "pb_clamped_glu": [_I, _P, _P, _I, _I, _F, _F, _P],
@@ -1105,6 +1106,11 @@ def selective_scan(ctx, x: torch.Tensor, xz: torch.Tensor, proj: torch.Tensor, w
                                   _p(a_log), _p(d_skip), _p(arena), arena.shape[1], int(tail_offset), _p(out), _p(ctx.cu_q),
                                   _p(ctx.state_slots), ctx.n_seqs, inner, n_state, dt_rank, int(n_taps), stream()),
           "selective_scan")
+
+
+def selective_scan_prompt_supported(n_state: int) -> bool:
+    """Whether ``selective_scan_prompt`` takes this state size."""
+    return bool(fn("pb_selective_scan_prompt_supported")(int(n_state)))
 
 
 def selective_scan_prompt(ctx, x: torch.Tensor, xz: torch.Tensor, bc: torch.Tensor, dt_pre: torch.Tensor, dt_bias: torch.Tensor,

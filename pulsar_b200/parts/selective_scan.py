@@ -79,7 +79,7 @@ class SelectiveScan(Mixer):
         x = ctx.scratch("scan.x", (n, self.inner))
         ops.causal_conv_silu(ctx, xz, self.inner, w["conv"], w["conv_bias"], cache.state, self.tail_offset, x)
         y = ctx.scratch("scan.y", (n, self.inner))
-        if n > PROMPT_MIN_TOKENS:
+        if n > PROMPT_MIN_TOKENS and ops.selective_scan_prompt_supported(self.n_state):
             # many tokens: the step sizes' product runs as a product (float32 out), and the scan kernel for portions takes
             # four tokens at a time (a function of the step's size alone; a captured step of single tokens never comes here)
             r = ctx.scratch("scan.r", (n, self.dt_rank))

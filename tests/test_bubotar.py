@@ -3,9 +3,12 @@ CPU; on a GPU each mechanism alone, prompts against token-by-token decoding, por
 state slots used again, crafted keys at the edges of chunks and pages, long decoding, and greedy generation through
 the public entry point."""
 import copy
+import json
 import math
 import os
 import random
+import subprocess
+import sys
 import types
 
 import pytest
@@ -537,3 +540,34 @@ def test_greedy_generation_through_the_engine(folders):
             row = plain.forward(cfg, w, seq, torch.float64)[-1]
             assert float(row.max() - row[tok]) <= TOL["bfloat16"] * float(row.abs().max())
             seq.append(tok)
+
+
+@gpu
+def test_command_line_and_trace_program(folders, tmp_path):
+    """The framework's two programs on a Bubotar folder: greedy tokens from bin/pulsar-generate, and logits from
+    bin/trace_run fed with steps on its standard input (a prompt in two portions, then single tokens)."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    raw, seed, page = CONFIGS["B"]
+    cfg, w = helpers.read_folder(folders["B"])
+    out = subprocess.run([sys.executable, os.path.join(root, "bin", "pulsar-generate"), "--model", folders["B"], "--dtype", "float32",
+                          "--prompt_ids", "5,4,3,2,1,0,7", "--prompt_ids", "9 8", "--gen_tokens", "6", "--max_pages", "64", "--eos_id",
+                          "-1", "--json"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    got = json.loads(out.stdout.strip().splitlines()[-1])["outputs"]
+    assert got == [plain.greedy_generate(cfg, w, p, 6) for p in ([5, 4, 3, 2, 1, 0, 7], [9, 8])]
+    rng = random.Random(3)
+    toks = helpers.random_tokens(rng, 40, raw["vocab"])
+    trace = helpers.Trace()
+    trace.step([("x", toks[:21], [20])])
+    trace.step([("x", toks[21:37], [0, 15])])
+    for i in range(37, 40):
+        trace.step([("x", toks[i:i + 1], [0])], end=["x"] if i == 39 else [])
+    run = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", folders["B"], "--dtype", "float32", "--out", str(tmp_path),
+                          "--max-tokens", "64"], input=trace.lines(), capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr
+    assert [ln for ln in run.stdout.splitlines() if ln.startswith("done ")] == [f"done {i}" for i in range(len(trace.records))]
+    ref = plain.forward(cfg, w, toks, torch.float64)
+    for i, rows in enumerate(trace.rows):
+        got = torch.from_file(str(tmp_path / f"{i}.f32"), size=len(rows) * raw["vocab"], dtype=torch.float32).view(len(rows), -1)
+        for j, (_, pos) in enumerate(rows):
+            assert helpers.rel_err(got[j], ref[pos]) < TOL["float32"]
