@@ -86,32 +86,24 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
     const int* table = block_table + (size_t)s * sh.table_stride;
 
     auto issue_kv = [&](int tile_index, int stage) {
+        // four threads per key row: one look into the block table, then the row's 16-byte pieces of K and of V
+        static_assert(kBN * 4 == kWarps * 32, "four threads per key row");
         const uint32_t k_dst = stage_base + stage * (kKBytes + kVBytes), v_dst = k_dst + kKBytes;
-        const int key0 = (kt0 + tile_index) * kBN;
-        for (int idx = tid; idx < kBN * kChunksK; idx += kWarps * 32) {
-            const int row = idx / kChunksK, c = idx % kChunksK;
-            const int key = key0 + row;
-            const bool ok = key >= lo_blk && key <= pos_last;
-            size_t at = 0;
-            if (ok) {
-                int page = table[key / sh.page_size];
-                if (!page_ok(page, bounds)) page = 0;
-                at = (((size_t)page * sh.Hkv + kvh) * sh.page_size + key % sh.page_size) * sh.k_stride + c * 8;
-            }
-            cp_async16(k_dst + tile_offset<DK>(row, c), k_pool + at, ok);
+        const int row = tid >> 2, sub = tid & 3;
+        const int key = (kt0 + tile_index) * kBN + row;
+        const bool ok = key >= lo_blk && key <= pos_last;
+        size_t k_at = 0, v_at = 0;
+        if (ok) {
+            int page = table[key / sh.page_size];
+            if (!page_ok(page, bounds)) page = 0;
+            const size_t at = ((size_t)page * sh.Hkv + kvh) * sh.page_size + key % sh.page_size;
+            k_at = at * sh.k_stride;
+            v_at = at * sh.v_stride;
         }
-        for (int idx = tid; idx < kBN * kChunksV; idx += kWarps * 32) {
-            const int row = idx / kChunksV, c = idx % kChunksV;
-            const int key = key0 + row;
-            const bool ok = key >= lo_blk && key <= pos_last;
-            size_t at = 0;
-            if (ok) {
-                int page = table[key / sh.page_size];
-                if (!page_ok(page, bounds)) page = 0;
-                at = (((size_t)page * sh.Hkv + kvh) * sh.page_size + key % sh.page_size) * sh.v_stride + c * 8;
-            }
-            cp_async16(v_dst + tile_offset<DV>(row, c), v_pool + at, ok);
-        }
+#pragma unroll
+        for (int c = sub; c < kChunksK; c += 4) cp_async16(k_dst + tile_offset<DK>(row, c), k_pool + k_at + c * 8, ok);
+#pragma unroll
+        for (int c = sub; c < kChunksV; c += 4) cp_async16(v_dst + tile_offset<DV>(row, c), v_pool + v_at + c * 8, ok);
     };
 
     issue_kv(0, 0);
