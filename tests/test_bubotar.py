@@ -429,14 +429,17 @@ def test_small_kernels_against_their_formulas(dtype):
     ops.heads_linear(a.cuda(), w_km, gated, gate.cuda()[:, 5:])
     close(gated, torch.einsum("nhk,hmk->nhm", a.double(), w.double()) * torch.sigmoid(gate[:, 5:].double()).view(n, H, M), "gated heads")
     # the norm behind a sublayer, the addition and the next norm in one kernel
-    width = 52
-    residual, delta = torch.randn(n, width, generator=g), rnd(n, width)
-    w_post, w_next = 1 + 0.1 * torch.randn(width, generator=g), 1 + 0.1 * torch.randn(width, generator=g)
-    res_dev, normed = residual.cuda(), torch.empty(n, width, dtype=dtype, device="cuda")
-    ops.post_norm_add(res_dev, delta.cuda(), w_post.cuda(), 1e-5, w_next.cuda(), 2e-5, normed)
-    want = residual.double() + plain.rms_norm(delta.double(), w_post.double(), 1e-5)
-    close(res_dev, want, "post_norm_add: the stream")
-    close(normed, plain.rms_norm(want, w_next.double(), 2e-5), "post_norm_add: the next norm")
+    for width in (52, 50, 4100):                # rows in registers (one and two vectors a thread), and the plain kernel
+        residual, delta = torch.randn(n, width, generator=g), rnd(n, width)
+        w_post, w_next = 1 + 0.1 * torch.randn(width, generator=g), 1 + 0.1 * torch.randn(width, generator=g)
+        res_dev, normed = residual.cuda(), torch.empty(n, width, dtype=dtype, device="cuda")
+        ops.post_norm_add(res_dev, delta.cuda(), w_post.cuda(), 1e-5, w_next.cuda(), 2e-5, normed)
+        want = residual.double() + plain.rms_norm(delta.double(), w_post.double(), 1e-5)
+        close(res_dev, want, f"post_norm_add ({width}): the stream")
+        close(normed, plain.rms_norm(want, w_next.double(), 2e-5), f"post_norm_add ({width}): the next norm")
+        res_dev = residual.cuda()
+        ops.post_norm_add(res_dev, delta.cuda(), w_post.cuda(), 1e-5)
+        close(res_dev, want, f"post_norm_add ({width}) without a next norm")
     # clamped gating
     gu = (3 * torch.randn(n, 2 * 18, generator=g)).to(dtype)
     act = torch.empty(n, 18, dtype=dtype, device="cuda")
