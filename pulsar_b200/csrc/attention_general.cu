@@ -492,6 +492,7 @@ template <typename T>
 __global__ void qkv_split_write_kernel(const T* __restrict__ qkv, float* __restrict__ q_out, T* __restrict__ k_pool,
                                        T* __restrict__ v_pool, const int* __restrict__ slots, int Hq, int Hkv, int Dk, int Dv,
                                        int page_size, const PoolBounds bounds) {
+    pdl_wait();         // may have come onto the SMs while the product before it was ending: nothing is touched before that one is done
     const int t = blockIdx.x, lane = threadIdx.x & 31;
     const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (head >= Hq + 2 * Hkv) return;
@@ -541,10 +542,10 @@ PB_EXPORT int pb_qkv_split_write(int dtype, const void* qkv, float* q_out, void*
     const int heads = Hq + 2 * Hkv;
     dim3 grid(n_tokens, (heads + 3) / 4);
     if (dtype == PB_F32)
-        qkv_split_write_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, q_out, (float*)k_pool, (float*)v_pool, slots, Hq,
+        launch_pdl(qkv_split_write_kernel<float>, grid, 128, 0, stream, (const float*)qkv, q_out, (float*)k_pool, (float*)v_pool, slots, Hq,
                                                                 Hkv, Dk, Dv, page_size, pb::pool_bounds_now());
     else if (dtype == PB_BF16)
-        qkv_split_write_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)qkv, q_out, (__nv_bfloat16*)k_pool,
+        launch_pdl(qkv_split_write_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)qkv, q_out, (__nv_bfloat16*)k_pool,
                                                                         (__nv_bfloat16*)v_pool, slots, Hq, Hkv, Dk, Dv, page_size,
                                                                         pb::pool_bounds_now());
     else return PB_ERR_BAD_DTYPE;

@@ -75,6 +75,7 @@ template <typename T, typename TO>
 __global__ void __launch_bounds__(128)
 heads_linear_kernel(const T* __restrict__ a, long a_tok, int a_head, const T* __restrict__ w, TO* __restrict__ out, long o_tok,
                     int o_head, const T* __restrict__ gate, long g_tok, int N, int M, int K) {
+    pdl_wait();         // may have come onto the SMs while the product before it was ending: nothing is touched before that one is done
     extern __shared__ __align__(16) float smem[];
     const int KS = (((K + kSlices - 1) / kSlices) + kBatch - 1) / kBatch * kBatch;      // k's per slice, a multiple of kBatch
     const int KP = KS * kSlices;
@@ -227,7 +228,7 @@ int launch_heads(const void* a, long a_tok, int a_head, const void* w, void* out
     }
     const int ks = (((K + kSlices - 1) / kSlices) + kBatch - 1) / kBatch * kBatch;
     dim3 grid((N + kTok - 1) / kTok, H, (M + 31) / 32);
-    heads_linear_kernel<T, TO><<<grid, 128, sizeof(float) * kTok * (ks * kSlices + kSlices * 32), stream>>>((const T*)a, a_tok, a_head, (const T*)w, (TO*)out,
+    launch_pdl(heads_linear_kernel<T, TO>, grid, 128, sizeof(float) * kTok * (ks * kSlices + kSlices * 32), stream, (const T*)a, a_tok, a_head, (const T*)w, (TO*)out,
                                                                                  o_tok, o_head, (const T*)gate, g_tok, N, M, K);
     return launch_status();
 }

@@ -60,6 +60,7 @@ template <typename T, int VPT>
 __global__ void post_norm_add_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ w_post,
                                          float eps_post, const float* __restrict__ w_next, float eps_next, T* __restrict__ out,
                                          int width) {
+    pdl_wait();         // may have come onto the SMs while the product before it was ending: nothing is touched before that one is done
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     float* res = residual + (size_t)r * width;
@@ -137,7 +138,7 @@ PB_EXPORT int pb_post_norm_add(int dtype, float* residual, const void* delta, co
         const int vecs = width / 4;
         const int vpt = vecs <= 1024 ? 1 : 2;
         const int threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;
-#define PB_POST(T, V) post_norm_add_vec_kernel<T, V><<<n, threads, 0, stream>>>(residual, (const T*)delta, w_post, eps_post, w_next, eps_next, (T*)out, width)
+#define PB_POST(T, V) launch_pdl(post_norm_add_vec_kernel<T, V>, n, threads, 0, stream, residual, (const T*)delta, w_post, eps_post, w_next, eps_next, (T*)out, width)
         if (dtype == PB_F32) { if (vpt == 1) PB_POST(float, 1); else PB_POST(float, 2); }
         else { if (vpt == 1) PB_POST(__nv_bfloat16, 1); else PB_POST(__nv_bfloat16, 2); }
 #undef PB_POST

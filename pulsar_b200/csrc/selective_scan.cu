@@ -37,6 +37,7 @@ causal_conv_silu_kernel(const T* __restrict__ in, long in_tok, const float* __re
                         const float* __restrict__ arena, long slot_stride, long tail_offset, const int* __restrict__ cu_q,
                         const int* __restrict__ seq_of_token, const int* __restrict__ state_slots, T* __restrict__ out,
                         int channels, int n_taps) {
+    pdl_wait();         // may have come onto the SMs while the product before it was ending: nothing is touched before that one is done
     const int t = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= channels) return;
@@ -69,6 +70,7 @@ selective_scan_kernel(const T* __restrict__ x, const T* __restrict__ xz, const T
                       const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                       float* __restrict__ arena, T* __restrict__ y, const int* __restrict__ cu_q,
                       const int* __restrict__ state_slots, const ScanShape sh) {
+    pdl_wait();         // may have come onto the SMs while the product before it was ending: nothing is touched before that one is done
     constexpr int CH = 128 / G;
     extern __shared__ float smem[];
     const int S = sh.n_state, R = sh.dt_rank, inner = sh.inner;
@@ -307,7 +309,7 @@ int launch_scan(const void* x, const void* xz, const void* proj, const void* w_d
     constexpr int CH = 128 / G;
     const size_t smem = sizeof(float) * kStage * (2 * sh.n_state + sh.dt_rank + 2 * CH);
     dim3 grid(n_seqs, (sh.inner + CH - 1) / CH);
-    selective_scan_kernel<T, G><<<grid, 128, smem, stream>>>((const T*)x, (const T*)xz, (const T*)proj, (const T*)w_dt, dt_bias,
+    launch_pdl(selective_scan_kernel<T, G>, grid, 128, smem, stream, (const T*)x, (const T*)xz, (const T*)proj, (const T*)w_dt, dt_bias,
                                                              a_log, d_skip, arena, (T*)y, cu_q, state_slots, sh);
     return launch_status();
 }
@@ -333,10 +335,10 @@ PB_EXPORT int pb_causal_conv_silu(int dtype, const void* in, long in_tok, const 
     dim3 grid(n_tokens, (channels + 255) / 256);
     if (grid.y > 65535) return PB_ERR_TOO_LARGE;
     if (dtype == PB_F32)
-        causal_conv_silu_kernel<float><<<grid, 256, 0, stream>>>((const float*)in, in_tok, taps, bias, arena, slot_stride, tail_offset,
+        launch_pdl(causal_conv_silu_kernel<float>, grid, 256, 0, stream, (const float*)in, in_tok, taps, bias, arena, slot_stride, tail_offset,
                                                                  cu_q, seq_of_token, state_slots, (float*)out, channels, n_taps);
     else if (dtype == PB_BF16)
-        causal_conv_silu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, in_tok, taps, bias, arena,
+        launch_pdl(causal_conv_silu_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)in, in_tok, taps, bias, arena,
                                                                          slot_stride, tail_offset, cu_q, seq_of_token, state_slots,
                                                                          (__nv_bfloat16*)out, channels, n_taps);
     else return PB_ERR_BAD_DTYPE;
