@@ -156,15 +156,23 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
                 uint32_t qh[4], ql[4];
                 ldmatrix_x4(qh, smem_base + tile_offset<DK>(q_row, ks * 2 + (lane >> 4)));
                 ldmatrix_x4(ql, smem_base + kQBytes + tile_offset<DK>(q_row, ks * 2 + (lane >> 4)));
+                // both halves of the queries against the tile's four groups of eight keys: eight MMAs, each accumulator
+                // used again only after three others
+                uint32_t kb[kBN / 16][4];
 #pragma unroll
                 for (int nn = 0; nn < kBN / 16; ++nn) {
-                    uint32_t kb[4];
                     const int row = nn * 16 + (lane & 7) + ((lane >> 4) << 3);
-                    ldmatrix_x4(kb, k_s + tile_offset<DK>(row, ks * 2 + ((lane >> 3) & 1)));
-                    mma_bf16(sc[2 * nn], qh, kb[0], kb[1]);
-                    mma_bf16(sc[2 * nn + 1], qh, kb[2], kb[3]);
-                    mma_bf16(sc[2 * nn], ql, kb[0], kb[1]);
-                    mma_bf16(sc[2 * nn + 1], ql, kb[2], kb[3]);
+                    ldmatrix_x4(kb[nn], k_s + tile_offset<DK>(row, ks * 2 + ((lane >> 3) & 1)));
+                }
+#pragma unroll
+                for (int nn = 0; nn < kBN / 16; ++nn) {
+                    mma_bf16(sc[2 * nn], qh, kb[nn][0], kb[nn][1]);
+                    mma_bf16(sc[2 * nn + 1], qh, kb[nn][2], kb[nn][3]);
+                }
+#pragma unroll
+                for (int nn = 0; nn < kBN / 16; ++nn) {
+                    mma_bf16(sc[2 * nn], ql, kb[nn][0], kb[nn][1]);
+                    mma_bf16(sc[2 * nn + 1], ql, kb[nn][2], kb[nn][3]);
                 }
             }
             // scores in the exponent's units (times log2 e), with the distance bias; what a row does not see is -inf
@@ -215,14 +223,19 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
                 split_bf16(pv[1][0], pv[1][1], ph[2], pl[2]);
                 split_bf16(pv[1][2], pv[1][3], ph[3], pl[3]);
 #pragma unroll
-                for (int i = 0; i < kNTiles; i += 2) {
-                    uint32_t vb[4];
+                for (int i = 0; i < kNTiles; i += 4) {
+                    uint32_t va[4], vb[4];
                     const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-                    ldmatrix_x4_trans(vb, v_s + tile_offset<DV>(row, i + (lane >> 4)));
-                    mma_bf16(o[i], ph, vb[0], vb[1]);
-                    mma_bf16(o[i + 1], ph, vb[2], vb[3]);
-                    mma_bf16(o[i], pl, vb[0], vb[1]);
-                    mma_bf16(o[i + 1], pl, vb[2], vb[3]);
+                    ldmatrix_x4_trans(va, v_s + tile_offset<DV>(row, i + (lane >> 4)));
+                    ldmatrix_x4_trans(vb, v_s + tile_offset<DV>(row, i + 2 + (lane >> 4)));
+                    mma_bf16(o[i], ph, va[0], va[1]);
+                    mma_bf16(o[i + 1], ph, va[2], va[3]);
+                    mma_bf16(o[i + 2], ph, vb[0], vb[1]);
+                    mma_bf16(o[i + 3], ph, vb[2], vb[3]);
+                    mma_bf16(o[i], pl, va[0], va[1]);
+                    mma_bf16(o[i + 1], pl, va[2], va[3]);
+                    mma_bf16(o[i + 2], pl, vb[0], vb[1]);
+                    mma_bf16(o[i + 3], pl, vb[2], vb[3]);
                 }
             }
         }
@@ -260,7 +273,7 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
 template <int DK, int DV>
 int launch_general_tc(const float* q, const void* k_pool, const void* v_pool, void* out, const int* block_table, const int* cu_q,
                       const int* kv_len, const float* slopes, int n_q_tiles, const TcShape& sh, cudaStream_t stream) {
-    static_assert(DV <= DK && DK % 16 == 0 && DV % 16 == 0 && DK >= 64 && DV >= 64, "tile shapes");
+    static_assert(DV <= DK && DK % 16 == 0 && DV % 32 == 0 && DK >= 64 && DV >= 64, "tile shapes");
     constexpr int smem = 2 * kBM * DK * 2 + 2 * kBN * (DK + DV) * 2;
     static bool configured = false;
     if (!configured) {
