@@ -287,6 +287,151 @@ int launch_scan_prompt(const void* x, const void* xz, const void* bc, long bc_to
     return launch_status();
 }
 
+// The scan for long portions, parallel over tokens.  For one channel and one state the recurrence S_t = a_t S_(t-1) + b_t
+// (a_t = exp(dt_t A), b_t = dt_t x_t B_t) composes: a run of tokens acts on the state as S -> P S + Q with P the product of
+// its a's and Q its own contribution.  A warp takes one channel and 256 tokens at a time: each lane walks its 8 consecutive
+// tokens to get (P, Q) of its run, the 32 runs are combined by a prefix scan over the lanes (five shuffle steps), each
+// lane takes the state that enters its run (the carried state of the span before, through the prefix of the lanes before
+// it) and walks its 8 tokens again to accumulate y_t += S_t C_t.  The states are taken one after the other, so a lane keeps
+// 8 step sizes, 8 inputs, 8 decays, 8 contributions and 8 outputs in registers.  A block of eight warps takes eight
+// neighbouring channels and shares the staged B and C rows of the span.  Tokens behind a portion's end enter as dt = 0
+// (a = 1, b = 0: they leave the state alone).  Shared-memory rows hold the span's tokens in the order [token in run][lane]
+// (one more word than 256 per row), so that lanes read neighbouring words and the staging writes hit different banks.
+constexpr int kSpan = 256, kRun = 8, kSpanRow = kSpan + 1, kChunkChannels = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+selective_scan_chunked_kernel(const T* __restrict__ x, const T* __restrict__ xz, const T* __restrict__ bc, long bc_tok,
+                              const float* __restrict__ dt_pre, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                              const float* __restrict__ d_skip, float* __restrict__ arena, T* __restrict__ y,
+                              const int* __restrict__ cu_q, const int* __restrict__ state_slots, const ScanShape sh) {
+    extern __shared__ float smem[];
+    const int S = sh.n_state, inner = sh.inner;
+    float* bc_s = smem;                                      // [2 S][kSpanRow]
+    float* x_s = bc_s + 2 * S * kSpanRow;                    // [8][kSpanRow]
+    float* z_s = x_s + kChunkChannels * kSpanRow;
+    float* dt_s = z_s + kChunkChannels * kSpanRow;
+    float* y_s = dt_s + kChunkChannels * kSpanRow;           // [8][kSpanRow]
+    float* a_s = y_s + kChunkChannels * kSpanRow;            // [8][S] decay rates A = -exp(A_log)
+    float* carry_s = a_s + kChunkChannels * S;               // [8][S] the state between spans
+
+    const int seq = blockIdx.x;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int c0 = blockIdx.y * kChunkChannels;
+    const int c = c0 + w;
+    const bool live = c < inner;
+    const int q0 = cu_q[seq], q_len = cu_q[seq + 1] - q0;
+    float* slot = arena + (size_t)state_slots[seq] * sh.slot_stride;
+    for (int n = lane; n < S; n += 32) {
+        a_s[w * S + n] = live ? -expf(a_log[(size_t)c * S + n]) : 0.0f;
+        carry_s[w * S + n] = live ? slot[(size_t)c * S + n] : 0.0f;
+    }
+    const float bias = live ? dt_bias[c] : 0.0f;
+    const float skip = live ? d_skip[c] : 0.0f;
+
+    for (int base = 0; base < q_len; base += kSpan) {
+        const int nt = min(kSpan, q_len - base);
+        __syncthreads();                                     // the span before is done with (and a_s, carry_s are written)
+        for (int i = threadIdx.x; i < kSpan * 2 * S; i += blockDim.x) {
+            const int tt = i / (2 * S), k = i % (2 * S);
+            const int at = (tt % kRun) * 32 + tt / kRun;     // [token in run][lane]
+            bc_s[k * kSpanRow + at] = tt < nt ? to_float(bc[(size_t)(q0 + base + tt) * bc_tok + k]) : 0.0f;
+        }
+        for (int i = threadIdx.x; i < kSpan * kChunkChannels; i += blockDim.x) {
+            const int tt = i / kChunkChannels, j = i % kChunkChannels;
+            const int at = (tt % kRun) * 32 + tt / kRun;
+            const bool on = tt < nt && c0 + j < inner;
+            const size_t row = (size_t)(q0 + base + (on ? tt : 0));
+            x_s[j * kSpanRow + at] = on ? to_float(x[row * inner + c0 + j]) : 0.0f;
+            z_s[j * kSpanRow + at] = on ? to_float(xz[row * sh.xz_tok + inner + c0 + j]) : 0.0f;
+            dt_s[j * kSpanRow + at] = on ? dt_pre[row * inner + c0 + j] : 0.0f;
+        }
+        __syncthreads();
+        float dt[kRun], dx[kRun], acc[kRun];
+#pragma unroll
+        for (int k = 0; k < kRun; ++k) {
+            const bool on = lane * kRun + k < nt;
+            dt[k] = on ? softplus_f(dt_s[w * kSpanRow + k * 32 + lane] + bias) : 0.0f;     // 0: the token leaves the state alone
+            dx[k] = dt[k] * x_s[w * kSpanRow + k * 32 + lane];
+            acc[k] = 0.0f;
+        }
+        for (int n = 0; n < S; ++n) {
+            const float rate = a_s[w * S + n];
+            const float* bn = bc_s + n * kSpanRow + lane;
+            const float* cn = bc_s + (S + n) * kSpanRow + lane;
+            float a[kRun], b[kRun];
+            float P = 1.0f, Q = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kRun; ++k) {
+                a[k] = expf(dt[k] * rate);
+                b[k] = dx[k] * bn[k * 32];
+                Q = fmaf(a[k], Q, b[k]);
+                P *= a[k];
+            }
+            // inclusive prefix over the lanes: (P, Q) of all runs up to and including this lane's
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float Pp = __shfl_up_sync(0xffffffffu, P, o), Qp = __shfl_up_sync(0xffffffffu, Q, o);
+                if (lane >= o) { Q = fmaf(P, Qp, Q); P *= Pp; }
+            }
+            const float carry = carry_s[w * S + n];
+            float Pe = __shfl_up_sync(0xffffffffu, P, 1), Qe = __shfl_up_sync(0xffffffffu, Q, 1);
+            if (lane == 0) { Pe = 1.0f; Qe = 0.0f; }
+            float st = fmaf(Pe, carry, Qe);                  // the state that enters this lane's run
+#pragma unroll
+            for (int k = 0; k < kRun; ++k) {
+                st = fmaf(a[k], st, b[k]);
+                acc[k] = fmaf(st, cn[k * 32], acc[k]);
+            }
+            const float P_all = __shfl_sync(0xffffffffu, P, 31), Q_all = __shfl_sync(0xffffffffu, Q, 31);
+            __syncwarp();                                    // every lane has read the carry
+            if (lane == 0) carry_s[w * S + n] = fmaf(P_all, carry, Q_all);
+        }
+#pragma unroll
+        for (int k = 0; k < kRun; ++k) {
+            const int at = k * 32 + lane;
+            y_s[w * kSpanRow + at] = (acc[k] + skip * x_s[w * kSpanRow + at]) * silu_f(z_s[w * kSpanRow + at]);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * kChunkChannels; i += blockDim.x) {
+            const int tt = i / kChunkChannels, j = i % kChunkChannels;
+            if (c0 + j < inner)
+                y[(size_t)(q0 + base + tt) * inner + c0 + j] = from_float<T>(y_s[j * kSpanRow + (tt % kRun) * 32 + tt / kRun]);
+        }
+    }
+    __syncwarp();
+    if (!live) return;
+    for (int n = lane; n < S; n += 32) slot[(size_t)c * S + n] = carry_s[w * S + n];
+    if (lane == 0) {
+        float* tail = slot + sh.tail_offset + (size_t)c * (sh.n_taps - 1);
+        for (int k = 0; k < sh.n_taps - 1; ++k) {
+            const int j = q_len - (sh.n_taps - 1) + k;
+            tail[k] = j >= 0 ? to_float(xz[(size_t)(q0 + j) * sh.xz_tok + c]) : tail[k + q_len];
+        }
+    }
+}
+
+size_t chunked_smem(int n_state) {
+    return sizeof(float) * ((size_t)(2 * n_state + 4 * kChunkChannels) * kSpanRow + 2 * kChunkChannels * n_state);
+}
+
+template <typename T>
+int launch_scan_chunked(const void* x, const void* xz, const void* bc, long bc_tok, const float* dt_pre, const float* dt_bias,
+                        const float* a_log, const float* d_skip, float* arena, void* y, const int* cu_q, const int* state_slots,
+                        int n_seqs, const ScanShape& sh, cudaStream_t stream) {
+    const size_t smem = chunked_smem(sh.n_state);
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        const cudaError_t e = cudaFuncSetAttribute(selective_scan_chunked_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        allowed = smem;
+    }
+    dim3 grid(n_seqs, (sh.inner + kChunkChannels - 1) / kChunkChannels);
+    selective_scan_chunked_kernel<T><<<grid, 256, smem, stream>>>((const T*)x, (const T*)xz, (const T*)bc, bc_tok, dt_pre, dt_bias, a_log,
+                                                                  d_skip, arena, (T*)y, cu_q, state_slots, sh);
+    return launch_status();
+}
+
 template <typename T>
 int dispatch_scan_prompt(const void* x, const void* xz, const void* bc, long bc_tok, const float* dt_pre, const float* dt_bias,
                          const float* a_log, const float* d_skip, float* arena, void* y, const int* cu_q, const int* state_slots,
@@ -388,5 +533,28 @@ PB_EXPORT int pb_selective_scan_prompt(int dtype, const void* x, const void* xz,
     if (dtype == PB_BF16)
         return dispatch_scan_prompt<__nv_bfloat16>(x, xz, bc, bc_tok, dt_pre, dt_bias, a_log, d_skip, arena, y, cu_q, state_slots,
                                                    n_seqs, sh, stream);
+    return PB_ERR_BAD_DTYPE;
+}
+
+// 1 when the scan that is parallel over tokens takes this state size (its staging of 256 tokens fits the shared memory).
+PB_EXPORT int pb_selective_scan_chunked_supported(int n_state) {
+    return (n_state > 0 && chunked_smem(n_state) <= 160 * 1024) ? 1 : 0;
+}
+
+// pb_selective_scan_prompt's arguments; the recurrence is evaluated 256 tokens at a time with a prefix scan over runs of 8.
+PB_EXPORT int pb_selective_scan_chunked(int dtype, const void* x, const void* xz, long xz_tok, const void* bc, long bc_tok,
+                                        const float* dt_pre, const float* dt_bias, const float* a_log, const float* d_skip,
+                                        float* arena, long slot_stride, long tail_offset, void* y, const int* cu_q,
+                                        const int* state_slots, int n_seqs, int inner, int n_state, int n_taps, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (inner <= 0 || n_state <= 0 || n_taps < 1) return PB_ERR_BAD_SIZE;
+    if (!pb_selective_scan_chunked_supported(n_state)) return PB_ERR_TOO_LARGE;
+    if ((inner + kChunkChannels - 1) / kChunkChannels > 65535) return PB_ERR_TOO_LARGE;
+    const ScanShape sh{inner, n_state, 0, n_taps, slot_stride, tail_offset, xz_tok, 0};
+    if (dtype == PB_F32)
+        return launch_scan_chunked<float>(x, xz, bc, bc_tok, dt_pre, dt_bias, a_log, d_skip, arena, y, cu_q, state_slots, n_seqs, sh, stream);
+    if (dtype == PB_BF16)
+        return launch_scan_chunked<__nv_bfloat16>(x, xz, bc, bc_tok, dt_pre, dt_bias, a_log, d_skip, arena, y, cu_q, state_slots, n_seqs,
+                                                  sh, stream);
     return PB_ERR_BAD_DTYPE;
 }

@@ -98,6 +98,8 @@ _SIGNATURES = {
     "pb_causal_conv_silu": [_I, _P, _L, _P, _P, _P, _L, _L, _P, _P, _P, _P, _I, _I, _I, _P],
     "pb_selective_scan": [_I, _P, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "pb_selective_scan_prompt_supported": [_I],
+    "pb_selective_scan_chunked_supported": [_I],
+    "pb_selective_scan_chunked": [_I, _P, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _P],
     "pb_selective_scan_prompt": [_I, _P, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _P],
     "pb_post_norm_add": [_I, _P, _P, _P, _F, _P, _F, _P, _I, _I, _P],
     "pb_clamped_glu": [_I, _P, _P, _I, _I, _F, _F, _P],
@@ -110,7 +112,7 @@ _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk
               "paged_attention_prefill_tc", "paged_attention_prefill_tcgen05", "gemm_skinny", "gemm_skinny_accumulate",
               "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update",
               "paged_attention_general", "paged_attention_general_tiled", "paged_attention_general_tc", "qkv_split_write", "heads_linear", "latent_prepare", "latent_expand_keys", "sigmoid_gate", "causal_conv_silu",
-              "selective_scan", "selective_scan_prompt", "post_norm_add", "clamped_glu"}
+              "selective_scan", "selective_scan_prompt", "selective_scan_chunked", "post_norm_add", "clamped_glu"}
 
 
 class KernelError(RuntimeError):
@@ -1113,11 +1115,18 @@ def selective_scan_prompt_supported(n_state: int) -> bool:
     return bool(fn("pb_selective_scan_prompt_supported")(int(n_state)))
 
 
+def selective_scan_chunked_supported(n_state: int) -> bool:
+    """Whether ``selective_scan_prompt(..., chunked=True)`` takes this state size."""
+    return bool(fn("pb_selective_scan_chunked_supported")(int(n_state)))
+
+
 def selective_scan_prompt(ctx, x: torch.Tensor, xz: torch.Tensor, bc: torch.Tensor, dt_pre: torch.Tensor, dt_bias: torch.Tensor,
                           a_log: torch.Tensor, d_skip: torch.Tensor, arena: torch.Tensor, tail_offset: int, n_taps: int,
-                          out: torch.Tensor) -> None:
+                          out: torch.Tensor, chunked: bool = False) -> None:
     """``selective_scan`` for steps with prompt portions: the step sizes' product was done beforehand (``dt_pre`` [N, inner]
-    float32 = r @ w_dt.T, before bias and softplus) and ``bc`` [N, 2 state] = [B | C] (or a tensor whose rows start so)."""
+    float32 = r @ w_dt.T, before bias and softplus) and ``bc`` [N, 2 state] = [B | C] (or a tensor whose rows start so).
+    ``chunked``: the kernel that is parallel over tokens (256 at a time, a prefix scan over runs of 8) instead of the one
+    that walks a portion token by token."""
     _cuda(x, xz, bc, dt_pre, dt_bias, a_log, d_skip, arena, out)
     n, inner = x.shape
     n_state = a_log.shape[1]
@@ -1125,10 +1134,10 @@ def selective_scan_prompt(ctx, x: torch.Tensor, xz: torch.Tensor, bc: torch.Tens
     assert x.dtype == xz.dtype == bc.dtype == out.dtype and out.shape == (n, inner)
     assert dt_pre.dtype == dt_bias.dtype == a_log.dtype == d_skip.dtype == arena.dtype == torch.float32 and a_log.shape[0] == inner
     assert arena.dim() == 2 and arena.shape[1] >= tail_offset + inner * (n_taps - 1) and tail_offset >= inner * n_state
-    check(fn("pb_selective_scan_prompt")(code(x.dtype), _p(x), _p(xz), xz.shape[1], _p(bc), bc.shape[1], _p(dt_pre), _p(dt_bias),
-                                         _p(a_log), _p(d_skip), _p(arena), arena.shape[1], int(tail_offset), _p(out), _p(ctx.cu_q),
-                                         _p(ctx.state_slots), ctx.n_seqs, inner, n_state, int(n_taps), stream()),
-          "selective_scan_prompt")
+    name = "pb_selective_scan_chunked" if chunked else "pb_selective_scan_prompt"
+    check(fn(name)(code(x.dtype), _p(x), _p(xz), xz.shape[1], _p(bc), bc.shape[1], _p(dt_pre), _p(dt_bias), _p(a_log), _p(d_skip),
+                   _p(arena), arena.shape[1], int(tail_offset), _p(out), _p(ctx.cu_q), _p(ctx.state_slots), ctx.n_seqs, inner,
+                   n_state, int(n_taps), stream()), name[3:])
 
 
 # ---------------------------------------------------------------- norms behind sublayers, clamped gating

@@ -1,6 +1,7 @@
 """The selective state-space mixer: input projection, short causal convolution, selective scan, gate, output projection."""
 from __future__ import annotations
 
+import os
 from typing import Dict, List
 
 import torch
@@ -11,7 +12,9 @@ from ..config.registry import MIXERS
 from ..config.specs import MixerSpec
 from .base import CacheView, Mixer, StepContext, WeightSpec
 
-PROMPT_MIN_TOKENS = 16      # steps of more tokens take the scan kernel for portions
+PROMPT_MIN_TOKENS = 16      # steps of more tokens take a scan kernel for portions ...
+CHUNKED_MIN_TOKENS = 32     # ... the one that is parallel over tokens where a portion has this many
+CHUNKED = os.environ.get("PULSAR_SCAN_CHUNKED", "1") != "0"
 
 
 @MIXERS.register("selective_scan")
@@ -79,9 +82,11 @@ class SelectiveScan(Mixer):
         x = ctx.scratch("scan.x", (n, self.inner))
         ops.causal_conv_silu(ctx, xz, self.inner, w["conv"], w["conv_bias"], cache.state, self.tail_offset, x)
         y = ctx.scratch("scan.y", (n, self.inner))
-        if n > PROMPT_MIN_TOKENS and ops.selective_scan_prompt_supported(self.n_state):
-            # many tokens: the step sizes' product runs as a product (float32 out), and the scan kernel for portions takes
-            # four tokens at a time (a function of the step's size alone; a captured step of single tokens never comes here)
+        chunked = CHUNKED and ctx.max_q_len >= CHUNKED_MIN_TOKENS and ops.selective_scan_chunked_supported(self.n_state)
+        if n > PROMPT_MIN_TOKENS and (chunked or ops.selective_scan_prompt_supported(self.n_state)):
+            # many tokens: the step sizes' product runs as a product (float32 out), and a scan kernel for portions follows:
+            # parallel over tokens where a portion is long, else eight tokens side by side (a captured step of single
+            # tokens never comes here)
             r = ctx.scratch("scan.r", (n, self.dt_rank))
             ops.linear(x, self.w_x_r, r)
             bc = ctx.scratch("scan.bc", (n, 2 * self.n_state))
@@ -89,7 +94,7 @@ class SelectiveScan(Mixer):
             dt_pre = ctx.scratch("scan.dt", (n, self.inner), torch.float32)
             ops.linear(r, w["dt"], dt_pre)
             ops.selective_scan_prompt(ctx, x, xz, bc, dt_pre, w["dt_bias"], w["a_log"], w["d"], cache.state, self.tail_offset,
-                                      self.taps, y)
+                                      self.taps, y, chunked=chunked)
         else:
             proj = ctx.scratch("scan.proj", (n, self.dt_rank + 2 * self.n_state))
             ops.linear(x, w["x"], proj)

@@ -526,6 +526,45 @@ def test_scan_kernels_carry_their_state_across_portions():
 
 
 @gpu
+@pytest.mark.parametrize("chunked", [False, True])
+def test_scan_kernels_for_portions(chunked):
+    """The two scan kernels for portions (step sizes from a product of their own) over three sequences of 1, 300 and 517
+    tokens with states carried in: against the recurrence written out token by token in float64."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(51)
+    inner, S, taps = 21, 12, 3
+    lens, slots = [1, 300, 517], [3, 0, 1]
+    arena = (0.3 * torch.randn(4, inner * (S + taps - 1), generator=g)).cuda()
+    start = arena.clone().cpu()
+    dt_b, d_skip = torch.randn(inner, generator=g) - 1, torch.randn(inner, generator=g)
+    a_log = torch.log(0.02 + 2 * torch.rand(inner, S, generator=g))            # slow decays too: far tokens stay in the state
+    n = sum(lens)
+    x, xz = torch.randn(n, inner, generator=g), torch.randn(n, 2 * inner, generator=g)
+    bc, dt_pre = torch.randn(n, 2 * S, generator=g), torch.randn(n, inner, generator=g)
+    want, at = [], 0
+    for L, slot in zip(lens, slots):
+        state = start[slot, :inner * S].view(inner, S).double()
+        for t in range(at, at + L):
+            dt = plain.softplus(dt_pre[t].double() + dt_b.double())
+            state = torch.exp(dt[:, None] * -torch.exp(a_log.double())) * state + (dt * x[t].double())[:, None] * bc[t, :S].double()[None]
+            want.append((state @ bc[t, S:].double() + d_skip.double() * x[t].double()) * plain.silu(xz[t, inner:].double()))
+        assert L < taps - 1 or True
+        at += L
+    want = torch.stack(want)
+    ctx = _step_context(lens, lens)
+    ctx.state_slots = torch.tensor(slots, dtype=torch.int32).cuda()
+    y = torch.empty(n, inner, device="cuda")
+    dev = lambda t: t.cuda().contiguous()
+    ops.selective_scan_prompt(ctx, dev(x), dev(xz), dev(bc), dev(dt_pre), dev(dt_b), dev(a_log), dev(d_skip), arena, inner * S, taps, y,
+                              chunked=chunked)
+    err = float((y.double().cpu() - want).abs().max() / want.abs().max())
+    assert err < 2e-5, f"{err:.3e}"
+    assert torch.equal(arena[2].cpu(), start[2])             # the slot nobody used
+    tail = arena[1, inner * S:].view(inner, taps - 1).cpu()      # the last inputs of the 517-token sequence
+    assert torch.equal(tail, xz[n - (taps - 1):, :inner].T.contiguous())
+
+
+@gpu
 def test_greedy_generation_through_the_engine(folders):
     from pulsar_b200.api import generate
     raw, seed, page = CONFIGS["A"]
