@@ -163,6 +163,7 @@ def own_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
     work["paged_attention_general_tc"] = (g * (2 * n * H * ((d + rot) * (4 + 2) + d * 4) + n * H * d * 6 + n * G * 2 * d * 2),
                                           g * (2 * 2.0 * H * (2 * d + rot) * lat_pairs + 2.0 * H * 2 * d * att_pairs), "bf16 tensor")
     work["selective_scan_prompt"] = (work["selective_scan"][0] + g * n * z["inner"] * 4, g * n * z["inner"] * 7.0 * z["state"], "fp32 FMA")
+    work["selective_scan_chunked"] = (work["selective_scan_prompt"][0], g * n * z["inner"] * 16.0 * z["state"], "fp32 FMA")
     work["latent_expand_keys"] = (g * 2 * n * H * (2 * d + rot) * 2, 0.0, "")
     work["sigmoid_gate"] = (g * 2 * n * H * d * 6, 0.0, "")
     return {k: (b * steps, f * steps, on) for k, (b, f, on) in work.items()}
