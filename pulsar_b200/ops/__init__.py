@@ -955,6 +955,7 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     assert block_table.dtype == torch.int32 and block_table.dim() == 2
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == hq)
     q_lens = ctx.host.q_lens
+    insist = tensor_cores is True
     if tensor_cores is None:
         tensor_cores = GENERAL_TC and max(q_lens) >= GENERAL_TC_MIN
     if tensor_cores:
@@ -968,6 +969,8 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
                                                       n_q_tiles, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale),
                                                       int(window or 0), int(chunk or 0), stream()), "paged_attention_general_tc")
             return
+        if insist:
+            raise KernelError("paged_attention_general: the tensor-core kernel does not take these sizes or dtypes")
     if tiled is None:
         tiled = GENERAL_TILED
     if tiled and fn("pb_attention_general_tiled_supported")(code(out.dtype), _p(k_pool), _p(v_pool), hq, hkv, dk, dv, k_stride,
