@@ -25,6 +25,9 @@ class PositionSpec:
     head_dim: int
     rotary_dim: int      # leading dims of each head that rotate (== head_dim for Qwen3)
     theta: float
+    # (factor, low, high, original): frequencies are rescaled by wavelength l = 2 pi / f: kept where l < original / high,
+    # divided by factor where l > original / low, and blended linearly in original / l between the two.  None: as they are.
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -45,6 +48,14 @@ class MixerSpec:
     chunk: Optional[int] = None      # c: a query at p sees only keys j with floor(j / c) == floor(p / c), chunks counted from 0
     distance_bias: Optional[float] = None   # r: the score loses 2^(-r (h+1) / n_heads) * (p - j) for head h; None: no bias
     tensor_names: Tuple[Tuple[str, str], ...] = ()   # role ("q", "k", "v", "o", ...) -> name behind the prefix, where not the default
+    keep_first: int = 0              # with a window or chunk: the first keep_first keys of a sequence stay visible all the same
+    softcap: Optional[float] = None  # c: the scaled score becomes c * tanh(score / c)
+    sinks: bool = False              # a learned number per head whose exponential joins the softmax's denominator (no key, no value)
+    bias: bool = False               # the q, k, v and o projections have biases (the weight's name + ".b" unless named by role)
+    output_gate: bool = False        # the concatenated heads are multiplied by sigmoid(W_g h) before the output projection
+    values_from_keys: bool = False   # no v projection: the value is the key as projected (before rotation and norm)
+    qk_norm_weight: bool = True      # False: q and k are divided by their root mean square (qk_norm_eps) without a weight
+    qk_norm_after_rotation: bool = False   # the per-head norm of q and k follows the rotation instead of preceding it
     extra: Tuple[Tuple[str, object], ...] = ()   # free-form parameters of other kinds
 
     def option(self, name, default=None):
@@ -78,7 +89,7 @@ class BlockSpec:
     kind: str
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]
-    mixer_norm: NormSpec
+    mixer_norm: Optional[NormSpec]          # None where the arrangement has no norm before the mixer ("postnorm")
     feed_forward_norm: Optional[NormSpec]
     weight_prefix: str                      # e.g. "model.layers.3."
     names: Tuple[Tuple[str, str], ...] = ()  # sub-prefixes: mixer, feed_forward, mixer_norm, feed_forward_norm (+ the post norms)

@@ -8,7 +8,10 @@
 //   * score = (q . k) * scale - slope[h] * (p - j) where `slopes` is given (a linear distance
 //     bias; p the query's position, j the key's);
 //   * visible keys lo .. p with lo the largest of 0, p - window + 1 (window > 0) and
-//     floor(p / chunk) * chunk (chunk > 0; chunks are counted from position 0 of the sequence).
+//     floor(p / chunk) * chunk (chunk > 0; chunks are counted from position 0 of the sequence);
+//     with keep_first > 0 the keys 0 .. keep_first - 1 stay visible below lo as well (at their true positions);
+//   * with softcap > 0 the scaled score becomes softcap * tanh(score / softcap) (before the distance bias);
+//   * with `sinks` [Hq] the softmax's denominator holds one more term per head, exp(sinks[h]), that has no value.
 // Queries come in float32 (rotation and score are 32-bit arithmetic whatever the cache holds);
 // scores, the running maximum, the sums and the output accumulate in float32 with expf.
 //
@@ -52,14 +55,26 @@ struct GeneralShape {
     int Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride;
     int k_vec;          // leading key elements that 16-byte loads may take (0 when rows are not 16-byte aligned)
     float scale;
+    int keep_first;     // keys below this stay visible whatever the window or chunk says; 0: none
+    float softcap;      // > 0: scaled scores are capped to softcap * tanh(score / softcap)
 };
+
+// Tiles of 32 keys that a query (or a block of queries) with lowest key `lo` walks over: the tiles that hold kept first
+// keys and lie wholly below the tile of `lo`, then the tiles from that of `lo` on.  n_kept is the count of the former.
+__device__ __forceinline__ int kept_tiles(int lo, int keep_first) {
+    return min((keep_first + 31) >> 5, lo >> 5);
+}
+__device__ __forceinline__ float cap_score(float s, float softcap) {
+    return softcap > 0.0f ? softcap * tanhf(s / softcap) : s;
+}
 
 template <typename T, int ACC>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_attention_general_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                                T* __restrict__ out, const int* __restrict__ block_table, const int* __restrict__ cu_q,
                                const int* __restrict__ kv_len, const int* __restrict__ seq_of_token,
-                               const float* __restrict__ slopes, const GeneralShape sh, const PoolBounds bounds) {
+                               const float* __restrict__ slopes, const float* __restrict__ sinks, const GeneralShape sh,
+                               const PoolBounds bounds) {
     extern __shared__ float smem[];
     const int Dk = sh.Dk, Dv = sh.Dv;
     float* q_s = smem;                         // [Dk] query times scale
@@ -90,9 +105,12 @@ paged_attention_general_kernel(const float* __restrict__ q, const T* __restrict_
     for (int i = 0; i < ACC; ++i) acc[i] = 0.0f;
 
     const int first_tile = lo >> 5, last_tile = p >> 5;
-    for (int tile = first_tile + warp; tile <= last_tile; tile += kWarps) {
+    const int n_kept = kept_tiles(lo, sh.keep_first);
+    const int n_walk = n_kept + last_tile - first_tile + 1;
+    for (int idx = warp; idx < n_walk; idx += kWarps) {
+        const int tile = idx < n_kept ? idx : first_tile + idx - n_kept;
         const int j = (tile << 5) + lane;
-        const bool valid = j >= lo && j <= p;
+        const bool valid = j <= p && (j >= lo || j < sh.keep_first);
         float sc = -INFINITY;
         if (valid) {
             int page = table[j / sh.page_size];
@@ -107,7 +125,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const T* __restrict_
                 for (int e = 0; e < Vec<T>::n; ++e) dot = fmaf(q_s[d + e], kf[e], dot);
             }
             for (; d < Dk; ++d) dot = fmaf(q_s[d], to_float(kr[d]), dot);
-            sc = dot - slope * (float)(p - j);
+            sc = cap_score(dot, sh.softcap) - slope * (float)(p - j);
         }
         const float m_new = fmaxf(m_run, warp_max(sc));      // finite: every tile in range has a visible key
         const float pv = valid ? expf(sc - m_new) : 0.0f;
@@ -120,10 +138,10 @@ paged_attention_general_kernel(const float* __restrict__ q, const T* __restrict_
         p_s[warp * 32 + lane] = pv;
         __syncwarp();
         const int j0 = tile << 5;
-        const int k_begin = (lo > j0) ? lo - j0 : 0;
         const int k_end = (p - j0 < 31) ? p - j0 : 31;
-        for (int kk = k_begin; kk <= k_end; ++kk) {
+        for (int kk = 0; kk <= k_end; ++kk) {
             const int jj = j0 + kk;
+            if (jj < lo && jj >= sh.keep_first) continue;      // uniform over the warp
             int page = table[jj / sh.page_size];
             if (!page_ok(page, bounds)) page = 0;
             const T* vr = v_pool + (((size_t)page * sh.Hkv + g) * sh.page_size + jj % sh.page_size) * sh.v_stride;
@@ -150,6 +168,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const T* __restrict_
     float f[kWarps];
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) { f[w] = (m_s[w] == -INFINITY) ? 0.0f : expf(m_s[w] - m_all); l_all += l_s[w] * f[w]; }
+    if (sinks) l_all += expf(sinks[h] - m_all);
     T* ov = out + ((size_t)t * sh.Hq + h) * Dv;
     for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
         float o = 0.0f;
@@ -161,22 +180,22 @@ paged_attention_general_kernel(const float* __restrict__ q, const T* __restrict_
 
 template <typename T, int ACC>
 int launch_general(const float* q, const void* k_pool, const void* v_pool, void* out, const int* block_table, const int* cu_q,
-                   const int* kv_len, const int* seq_of_token, const float* slopes, int n_tokens, const GeneralShape& sh,
-                   cudaStream_t stream) {
+                   const int* kv_len, const int* seq_of_token, const float* slopes, const float* sinks, int n_tokens,
+                   const GeneralShape& sh, cudaStream_t stream) {
     const size_t smem = sizeof(float) * (sh.Dk + kWarps * 32 + 2 * kWarps + (size_t)kWarps * sh.Dv);
     dim3 grid(n_tokens, sh.Hq);
     paged_attention_general_kernel<T, ACC><<<grid, kWarps * 32, smem, stream>>>(q, (const T*)k_pool, (const T*)v_pool, (T*)out,
-        block_table, cu_q, kv_len, seq_of_token, slopes, sh, pb::pool_bounds_now());
+        block_table, cu_q, kv_len, seq_of_token, slopes, sinks, sh, pb::pool_bounds_now());
     return launch_status();
 }
 
 template <typename T>
 int dispatch_general(const float* q, const void* k_pool, const void* v_pool, void* out, const int* block_table, const int* cu_q,
-                     const int* kv_len, const int* seq_of_token, const float* slopes, int n_tokens, GeneralShape sh,
-                     cudaStream_t stream) {
+                     const int* kv_len, const int* seq_of_token, const float* slopes, const float* sinks, int n_tokens,
+                     GeneralShape sh, cudaStream_t stream) {
     const bool aligned = ((uintptr_t)k_pool % 16 == 0) && ((size_t)sh.k_stride * sizeof(T)) % 16 == 0;
     sh.k_vec = aligned ? sh.Dk - sh.Dk % Vec<T>::n : 0;
-#define PB_GENERAL(A) return launch_general<T, A>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token, slopes, n_tokens, sh, stream)
+#define PB_GENERAL(A) return launch_general<T, A>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token, slopes, sinks, n_tokens, sh, stream)
     if (sh.Dv <= 64) PB_GENERAL(2);
     if (sh.Dv <= 128) PB_GENERAL(4);
     if (sh.Dv <= 256) PB_GENERAL(8);
@@ -210,8 +229,8 @@ template <typename T, int ACC>
 __global__ void __launch_bounds__(128)
 general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool, T* __restrict__ out,
                      float* __restrict__ partial, const int* __restrict__ block_table, const int* __restrict__ cu_q,
-                     const int* __restrict__ kv_len, const float* __restrict__ slopes, const TiledShape ts,
-                     const PoolBounds bounds) {
+                     const int* __restrict__ kv_len, const float* __restrict__ slopes, const float* __restrict__ sinks,
+                     const TiledShape ts, const PoolBounds bounds) {
     constexpr int V = Vec<T>::n;
     const GeneralShape& sh = ts.g;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -247,9 +266,11 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
         lo_blk = min(lo_blk, lo);
         hi_blk = max(hi_blk, p);
     }
-    const int kt0 = lo_blk / kTile, n_tiles = hi_blk / kTile - kt0 + 1;
+    // the tiles the block walks over, in ascending order: those of kept first keys below the span, then the span's
+    const int kt0 = lo_blk / kTile, n_kept = kept_tiles(lo_blk, sh.keep_first);
+    const int n_tiles = n_kept + hi_blk / kTile - kt0 + 1;
     const int per = (n_tiles + ts.n_splits - 1) / ts.n_splits;
-    const int t_begin = kt0 + split * per, t_end = min(kt0 + n_tiles, t_begin + per);
+    const int t_begin = split * per, t_end = min(n_tiles, t_begin + per);
 
     // this thread's four rows
     int pos[4], lo_r[4], tok[4], head[4];
@@ -291,14 +312,15 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
     }
 
     const int k_chunks = Dk / V, v_chunks = Dv / V;
-    for (int kt = t_begin; kt < t_end; ++kt) {
+    for (int ti = t_begin; ti < t_end; ++ti) {
+        const int kt = ti < n_kept ? ti : kt0 + ti - n_kept;
         const int j0 = kt * kTile;
         __syncthreads();                                   // the tile before is done with
         {
             // four threads per key: one look into the block table, then the row's 16-byte pieces, all in flight at once
             const int key = threadIdx.x >> 2, sub = threadIdx.x & 3;
             const int j = j0 + key;
-            const bool ok = j >= lo_blk && j <= hi_blk;        // rows outside the block's span are filled with zeros
+            const bool ok = j <= hi_blk && (j >= lo_blk || j < sh.keep_first);   // rows outside the block's span are filled with zeros
             const T* k_src = k_pool;
             const T* v_src = v_pool;
             if (ok) {
@@ -340,8 +362,10 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
         const int j = j0 + lane;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            const bool vis = j >= lo_r[r] && j <= pos[r];
-            const float v = vis ? fmaf(sc[r], sh.scale, -slope[r] * (float)(pos[r] - j)) : -INFINITY;
+            const bool vis = j <= pos[r] && (j >= lo_r[r] || j < sh.keep_first);
+            const float v = vis ? (sh.softcap > 0.0f ? cap_score(sc[r] * sh.scale, sh.softcap) - slope[r] * (float)(pos[r] - j)
+                                                     : fmaf(sc[r], sh.scale, -slope[r] * (float)(pos[r] - j)))
+                                : -INFINITY;
             const float m_new = fmaxf(m_run[r], warp_max(v));
             float pv = 0.0f, corr = 1.0f;
             if (m_new != -INFINITY) {                       // uniform over the warp
@@ -389,7 +413,7 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
         const size_t row = (size_t)tok[r] * sh.Hq + head[r];
         if (ts.n_splits == 1) {
             T* ov = out + row * Dv;
-            const float inv = 1.0f / l_run[r];
+            const float inv = 1.0f / (sinks ? l_run[r] + expf(sinks[head[r]] - m_run[r]) : l_run[r]);
 #pragma unroll
             for (int i = 0; i < ACC; ++i) {
                 const int c = lane + 32 * i;
@@ -410,7 +434,8 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
 // out[row] = sum over the splits, in their order, of their partial outputs weighted by exp(m_split - m_all), over the
 // weighted sum of their sums.  One block per (token, head).
 template <typename T>
-__global__ void general_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int n_splits, int Dv) {
+__global__ void general_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, const float* __restrict__ sinks,
+                                       int Hq, int n_splits, int Dv) {
     const size_t row = blockIdx.x;
     const float* pp = partial + row * n_splits * (Dv + 2);
     float m_all = -INFINITY;
@@ -420,6 +445,7 @@ __global__ void general_combine_kernel(const float* __restrict__ partial, T* __r
         const float m = pp[(size_t)z * (Dv + 2)];
         if (m != -INFINITY) l_all += pp[(size_t)z * (Dv + 2) + 1] * expf(m - m_all);
     }
+    if (sinks) l_all += expf(sinks[row % Hq] - m_all);
     for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
         float o = 0.0f;
         for (int z = 0; z < n_splits; ++z) {
@@ -437,8 +463,8 @@ size_t tiled_smem(const TiledShape& ts) {
 
 template <typename T, int ACC>
 int launch_tiled(const float* q, const void* k_pool, const void* v_pool, void* out, float* partial, const int* block_table,
-                 const int* cu_q, const int* kv_len, const float* slopes, int n_tokens, int row_tiles, const TiledShape& ts,
-                 cudaStream_t stream) {
+                 const int* cu_q, const int* kv_len, const float* slopes, const float* sinks, int n_tokens, int row_tiles,
+                 const TiledShape& ts, cudaStream_t stream) {
     const size_t smem = tiled_smem<T>(ts);
     static size_t allowed = 48 * 1024;                     // per instantiation
     if (smem > allowed) {
@@ -448,12 +474,12 @@ int launch_tiled(const float* q, const void* k_pool, const void* v_pool, void* o
     }
     dim3 grid(row_tiles, ts.g.Hkv, ts.n_splits);
     general_tiled_kernel<T, ACC><<<grid, 128, smem, stream>>>(q, (const T*)k_pool, (const T*)v_pool, (T*)out, partial, block_table,
-                                                              cu_q, kv_len, slopes, ts, pb::pool_bounds_now());
+                                                              cu_q, kv_len, slopes, sinks, ts, pb::pool_bounds_now());
     int status = launch_status();
     if (status == 0 && ts.n_splits > 1) {
         int b = 32;
         while (b < ts.g.Dv && b < 256) b <<= 1;
-        general_combine_kernel<T><<<n_tokens * ts.g.Hq, b, 0, stream>>>(partial, (T*)out, ts.n_splits, ts.g.Dv);
+        general_combine_kernel<T><<<n_tokens * ts.g.Hq, b, 0, stream>>>(partial, (T*)out, sinks, ts.g.Hq, ts.n_splits, ts.g.Dv);
         status = launch_status();
     }
     return status;
@@ -476,9 +502,9 @@ bool tiled_shape(TiledShape& ts, const void* k_pool, const void* v_pool) {
 
 template <typename T>
 int dispatch_tiled(const float* q, const void* k_pool, const void* v_pool, void* out, float* partial, const int* block_table,
-                   const int* cu_q, const int* kv_len, const float* slopes, int n_tokens, int row_tiles, const TiledShape& ts,
-                   cudaStream_t stream) {
-#define PB_TILED(A) return launch_tiled<T, A>(q, k_pool, v_pool, out, partial, block_table, cu_q, kv_len, slopes, n_tokens, row_tiles, ts, stream)
+                   const int* cu_q, const int* kv_len, const float* slopes, const float* sinks, int n_tokens, int row_tiles,
+                   const TiledShape& ts, cudaStream_t stream) {
+#define PB_TILED(A) return launch_tiled<T, A>(q, k_pool, v_pool, out, partial, block_table, cu_q, kv_len, slopes, sinks, n_tokens, row_tiles, ts, stream)
     if (ts.g.Dv <= 64) PB_TILED(2);
     if (ts.g.Dv <= 128) PB_TILED(4);
     if (ts.g.Dv <= 256) PB_TILED(8);
@@ -520,18 +546,19 @@ PB_EXPORT int pb_paged_attention_general(int dtype, const float* q, const void* 
                                          const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                                          const int* seq_of_token, const float* slopes, int n_tokens, int Hq, int Hkv, int Dk,
                                          int Dv, int k_stride, int v_stride, int page_size, float scale, int window, int chunk,
-                                         cudaStream_t stream) {
+                                         int keep_first, float softcap, const float* sinks, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (Dk <= 0 || Dv <= 0 || Dk > 4096 || Dv > 1024 || Hkv <= 0 || Hq <= 0 || Hq % Hkv || page_size <= 0 || k_stride < Dk ||
-        v_stride < Dv || window < 0 || chunk < 0)
+        v_stride < Dv || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f))
         return PB_ERR_BAD_SIZE;
     if (Hq > 65535) return PB_ERR_TOO_LARGE;
-    GeneralShape sh{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale};
+    GeneralShape sh{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap};
     if (dtype == PB_F32)
-        return dispatch_general<float>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token, slopes, n_tokens, sh, stream);
+        return dispatch_general<float>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token, slopes, sinks, n_tokens, sh,
+                                       stream);
     if (dtype == PB_BF16)
-        return dispatch_general<__nv_bfloat16>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token, slopes, n_tokens, sh,
-                                               stream);
+        return dispatch_general<__nv_bfloat16>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token, slopes, sinks, n_tokens,
+                                               sh, stream);
     return PB_ERR_BAD_DTYPE;
 }
 
@@ -557,7 +584,7 @@ PB_EXPORT int pb_attention_general_tiled_supported(int dtype, const void* k_pool
                                                    int k_stride, int v_stride) {
     if (Dk <= 0 || Dv <= 0 || Dv > 512 || Hkv <= 0 || Hq <= 0 || Hq % Hkv || k_stride < Dk || v_stride < Dv) return 0;
     TiledShape ts{};
-    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, 1, 0, 0, 0, 0, 1.0f};
+    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, 1, 0, 0, 0, 0, 1.0f, 0, 0.0f};
     if (dtype == PB_F32) return tiled_shape<float>(ts, k_pool, v_pool) ? 1 : 0;
     if (dtype == PB_BF16) return tiled_shape<__nv_bfloat16>(ts, k_pool, v_pool) ? 1 : 0;
     return 0;
@@ -569,22 +596,24 @@ PB_EXPORT int pb_paged_attention_general_tiled(int dtype, const float* q, const 
                                                float* partial, const int* block_table, int table_stride, const int* cu_q,
                                                const int* kv_len, const float* slopes, int n_tokens, int n_seqs, int row_tiles,
                                                int n_splits, int Hq, int Hkv, int Dk, int Dv, int k_stride, int v_stride,
-                                               int page_size, float scale, int window, int chunk, cudaStream_t stream) {
+                                               int page_size, float scale, int window, int chunk, int keep_first, float softcap,
+                                               const float* sinks, cudaStream_t stream) {
     if (n_tokens <= 0 || row_tiles <= 0) return 0;
     if (!pb_attention_general_tiled_supported(dtype, k_pool, v_pool, Hq, Hkv, Dk, Dv, k_stride, v_stride)) return PB_ERR_BAD_SIZE;
-    if (page_size <= 0 || window < 0 || chunk < 0 || n_splits < 1 || n_splits > 65535 || (n_splits > 1 && partial == nullptr) ||
-        (uintptr_t)q % 16)
+    if (page_size <= 0 || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f) || n_splits < 1 || n_splits > 65535 ||
+        (n_splits > 1 && partial == nullptr) || (uintptr_t)q % 16)
         return PB_ERR_BAD_SIZE;
     if (Hkv > 65535) return PB_ERR_TOO_LARGE;
     TiledShape ts{};
-    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale};
+    ts.g = GeneralShape{Hq, Hkv, Dk, Dv, k_stride, v_stride, page_size, window, chunk, table_stride, 0, scale, keep_first, softcap};
     ts.n_seqs = n_seqs;
     ts.n_splits = n_splits;
     if (dtype == PB_F32) {
         tiled_shape<float>(ts, k_pool, v_pool);
-        return dispatch_tiled<float>(q, k_pool, v_pool, out, partial, block_table, cu_q, kv_len, slopes, n_tokens, row_tiles, ts, stream);
+        return dispatch_tiled<float>(q, k_pool, v_pool, out, partial, block_table, cu_q, kv_len, slopes, sinks, n_tokens, row_tiles, ts,
+                                     stream);
     }
     tiled_shape<__nv_bfloat16>(ts, k_pool, v_pool);
-    return dispatch_tiled<__nv_bfloat16>(q, k_pool, v_pool, out, partial, block_table, cu_q, kv_len, slopes, n_tokens, row_tiles, ts,
-                                         stream);
+    return dispatch_tiled<__nv_bfloat16>(q, k_pool, v_pool, out, partial, block_table, cu_q, kv_len, slopes, sinks, n_tokens, row_tiles,
+                                         ts, stream);
 }

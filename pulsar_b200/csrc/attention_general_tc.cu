@@ -12,6 +12,9 @@
 // queries stay in shared memory; keys and values stream through a two-stage cp.async pipeline of 32-key tiles
 // gathered row by row through the block table (any page size) into XOR-swizzled tiles.  Tiles are aligned to
 // absolute key indices and taken in ascending order; a tile in which a row sees nothing leaves the row as it was.
+// Kept first keys (keep_first > 0: keys 0 .. keep_first - 1 stay visible below the window), a cap on the scaled score
+// (softcap > 0: softcap * tanh(score / softcap), tanhf in float32) and a sink per head (one more term exp(sinks[h]) in
+// the softmax's denominator) as in the CUDA-core kernels.
 // Sizes: (key width, value width) = (64, 64), (128, 128), (192, 128); everything else takes the CUDA-core kernels.
 #include "mma_common.cuh"
 
@@ -40,6 +43,8 @@ __device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint3
 struct TcShape {
     int n_seqs, Hq, Hkv, k_stride, v_stride, page_size, window, chunk, table_stride;
     float scale;
+    int keep_first;
+    float softcap;
 };
 
 __device__ __forceinline__ int lowest_key(int pos, const TcShape& sh) {
@@ -53,7 +58,8 @@ template <int DK, int DV>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                   bf16* __restrict__ out, const int* __restrict__ block_table, const int* __restrict__ cu_q,
-                  const int* __restrict__ kv_len, const float* __restrict__ slopes, const TcShape sh, const PoolBounds bounds) {
+                  const int* __restrict__ kv_len, const float* __restrict__ slopes, const float* __restrict__ sinks,
+                  const TcShape sh, const PoolBounds bounds) {
     constexpr int kChunksK = DK / 8, kChunksV = DV / 8;
     constexpr int kQBytes = kBM * DK * 2;                    // one of the two query tiles
     constexpr int kKBytes = kBN * DK * 2, kVBytes = kBN * DV * 2;
@@ -82,7 +88,9 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
     const int ctx0 = kv_len[s] - q_len;
     const int pos_first = ctx0 + m0, pos_last = ctx0 + m0 + rows - 1;
     const int lo_blk = lowest_key(pos_first, sh);            // the lowest key is no lower for a later position
-    const int kt0 = lo_blk / kBN, n_tiles = pos_last / kBN - kt0 + 1;
+    // the tiles the block walks over, in ascending order: those of kept first keys below the span, then the span's
+    const int kt0 = lo_blk / kBN, n_kept = min((sh.keep_first + kBN - 1) / kBN, kt0);
+    const int n_tiles = n_kept + pos_last / kBN - kt0 + 1;
     const int* table = block_table + (size_t)s * sh.table_stride;
 
     auto issue_kv = [&](int tile_index, int stage) {
@@ -90,8 +98,8 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
         static_assert(kBN * 4 == kWarps * 32, "four threads per key row");
         const uint32_t k_dst = stage_base + stage * (kKBytes + kVBytes), v_dst = k_dst + kKBytes;
         const int row = tid >> 2, sub = tid & 3;
-        const int key = (kt0 + tile_index) * kBN + row;
-        const bool ok = key >= lo_blk && key <= pos_last;
+        const int key = (tile_index < n_kept ? tile_index : kt0 + tile_index - n_kept) * kBN + row;
+        const bool ok = key <= pos_last && (key >= lo_blk || key < sh.keep_first);
         size_t k_at = 0, v_at = 0;
         if (ok) {
             int page = table[key / sh.page_size];
@@ -145,8 +153,8 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
 
         const int stage = it & 1;
         const uint32_t k_s = stage_base + stage * (kKBytes + kVBytes), v_s = k_s + kKBytes;
-        const int key0 = (kt0 + it) * kBN;
-        const bool active = warp * 16 < rows && key0 <= wpos_last && key0 + kBN - 1 >= wlo_first;
+        const int key0 = (it < n_kept ? it : kt0 + it - n_kept) * kBN;
+        const bool active = warp * 16 < rows && key0 <= wpos_last && (key0 + kBN - 1 >= wlo_first || key0 < sh.keep_first);
         if (active) {
             float sc[kBN / 8][4];
 #pragma unroll
@@ -184,8 +192,14 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
                     const int key = key0 + n * 8 + 2 * t + (e & 1);
                     const int pos = (e >> 1) ? pos1 : pos0;
                     const int lo = (e >> 1) ? lo1 : lo0;
-                    const bool vis = key <= pos && key >= lo;
-                    const float v = vis ? fmaf(sc[n][e], sl2, -slope2 * (float)(pos - key)) : -INFINITY;
+                    const bool vis = key <= pos && (key >= lo || key < sh.keep_first);
+                    float v = -INFINITY;
+                    if (vis) {
+                        if (sh.softcap > 0.0f)
+                            v = fmaf(sh.softcap * tanhf(sc[n][e] * sh.scale / sh.softcap), kLog2e, -slope2 * (float)(pos - key));
+                        else
+                            v = fmaf(sc[n][e], sl2, -slope2 * (float)(pos - key));
+                    }
                     sc[n][e] = v;
                     tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
                 }
@@ -248,6 +262,7 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
     for (int r = 0; r < 2; ++r) {
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+        if (sinks != nullptr && m_run[r] != -INFINITY) l_run[r] += ex2(fmaf(sinks[head], kLog2e, -m_run[r]));
     }
     const float inv0 = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, inv1 = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
     unsigned char* w_s = smem + warp * 16 * DK * 2;          // [16 rows][DV] bf16, swizzled; DV <= DK
@@ -272,7 +287,8 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
 
 template <int DK, int DV>
 int launch_general_tc(const float* q, const void* k_pool, const void* v_pool, void* out, const int* block_table, const int* cu_q,
-                      const int* kv_len, const float* slopes, int n_q_tiles, const TcShape& sh, cudaStream_t stream) {
+                      const int* kv_len, const float* slopes, const float* sinks, int n_q_tiles, const TcShape& sh,
+                      cudaStream_t stream) {
     static_assert(DV <= DK && DK % 16 == 0 && DV % 32 == 0 && DK >= 64 && DV >= 64, "tile shapes");
     constexpr int smem = 2 * kBM * DK * 2 + 2 * kBN * (DK + DV) * 2;
     static bool configured = false;
@@ -283,7 +299,7 @@ int launch_general_tc(const float* q, const void* k_pool, const void* v_pool, vo
     }
     dim3 grid(n_q_tiles, sh.Hq);
     general_tc_kernel<DK, DV><<<grid, kWarps * 32, smem, stream>>>(q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table,
-                                                                   cu_q, kv_len, slopes, sh, pool_bounds_now());
+                                                                   cu_q, kv_len, slopes, sinks, sh, pool_bounds_now());
     return launch_status();
 }
 
@@ -306,13 +322,15 @@ PB_EXPORT int pb_paged_attention_general_tc(int dtype, const float* q, const voi
                                             const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                                             const float* slopes, int n_seqs, int n_q_tiles, int Hq, int Hkv, int Dk, int Dv,
                                             int k_stride, int v_stride, int page_size, float scale, int window, int chunk,
-                                            cudaStream_t stream) {
+                                            int keep_first, float softcap, const float* sinks, cudaStream_t stream) {
     if (n_seqs <= 0 || n_q_tiles <= 0) return 0;
     if (!pb_attention_general_tc_supported(dtype, q, k_pool, v_pool, Hq, Hkv, Dk, Dv, k_stride, v_stride) || ((uintptr_t)out % 16))
         return PB_ERR_BAD_SIZE;
-    if (page_size <= 0 || window < 0 || chunk < 0) return PB_ERR_BAD_SIZE;
-    const TcShape sh{n_seqs, Hq, Hkv, k_stride, v_stride, page_size, window, chunk, table_stride, scale};
-    if (Dk == 64) return launch_general_tc<64, 64>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, n_q_tiles, sh, stream);
-    if (Dk == 128) return launch_general_tc<128, 128>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, n_q_tiles, sh, stream);
-    return launch_general_tc<192, 128>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, n_q_tiles, sh, stream);
+    if (page_size <= 0 || window < 0 || chunk < 0 || keep_first < 0 || !(softcap >= 0.0f)) return PB_ERR_BAD_SIZE;
+    const TcShape sh{n_seqs, Hq, Hkv, k_stride, v_stride, page_size, window, chunk, table_stride, scale, keep_first, softcap};
+    if (Dk == 64)
+        return launch_general_tc<64, 64>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, sinks, n_q_tiles, sh, stream);
+    if (Dk == 128)
+        return launch_general_tc<128, 128>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, sinks, n_q_tiles, sh, stream);
+    return launch_general_tc<192, 128>(q, k_pool, v_pool, out, block_table, cu_q, kv_len, slopes, sinks, n_q_tiles, sh, stream);
 }

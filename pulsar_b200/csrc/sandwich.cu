@@ -6,6 +6,11 @@
 //   clamped_glu      gate_up [N, 2I] (gate columns, then up columns) -> out [N, I]:
 //                    g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1),
 //                    float32 arithmetic, one rounding on store.
+//   post_norm_add_bias   the same for layers whose sublayers read the stream itself: residual += rmsnorm(delta + bias) *
+//                    w_post (bias optional: the bias of the projection that made delta), and out = the stream as it
+//                    now is, in the activation dtype, for the sublayer that reads it next.  Without delta: out only.
+//   glu_bias         gate_up [N, 2I] + bias [2I] -> out [N, I] with the gating of the fused products (limit, alpha,
+//                    shift; SwiGLU is inf, 1, 0): the gated unit of a feed-forward whose projections have biases.
 #include "common.cuh"
 
 #include <stdint.h>
@@ -120,6 +125,45 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gate_up, T* __restrict_
     }
 }
 
+template <typename T>
+__global__ void post_norm_add_bias_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ bias,
+                                          const float* __restrict__ w_post, float eps_post, T* __restrict__ out, int width) {
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float* res = residual + (size_t)r * width;
+    if (delta != nullptr) {                       // uniform over the grid
+        const T* del = delta + (size_t)r * width;
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float d = to_float(del[i]) + (bias ? bias[i] : 0.0f);
+            ss += d * d;
+        }
+        const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps_post);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float d = to_float(del[i]) + (bias ? bias[i] : 0.0f);
+            const float x = res[i] + d * inv * w_post[i];
+            res[i] = x;
+            if (out != nullptr) out[(size_t)r * width + i] = from_float<T>(x);
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)r * width + i] = from_float<T>(res[i]);
+}
+
+template <typename TIn, typename T>
+__global__ void glu_bias_kernel(const TIn* __restrict__ gate_up, const float* __restrict__ bias, T* __restrict__ out, size_t total,
+                                const GatedInter p) {
+    pdl_wait();
+    const int inter = p.n;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / inter, col = i % inter;
+        const float g = to_float(gate_up[row * 2 * inter + col]) + (bias ? bias[col] : 0.0f);
+        const float u = to_float(gate_up[row * 2 * inter + inter + col]) + (bias ? bias[inter + col] : 0.0f);
+        out[i] = from_float<T>(gated(g, u, p));
+    }
+}
+
 int block_for(int width) {
     int b = 32;
     while (b < 1024 && b * 4 < width) b <<= 1;
@@ -169,4 +213,39 @@ PB_EXPORT int pb_clamped_glu(int dtype, const void* gate_up, void* out, int n, i
                                                                            total, limit, alpha);
     else return PB_ERR_BAD_DTYPE;
     return launch_status();
+}
+
+// residual [n, width] float32 += rmsnorm(delta + bias) * w_post, and out [n, width] (dtype) = residual where out is given;
+// delta null: out = residual only (bias, w_post unused).
+PB_EXPORT int pb_post_norm_add_bias(int dtype, float* residual, const void* delta, const float* bias, const float* w_post,
+                                    float eps_post, void* out, int n, int width, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (width <= 0 || (delta == nullptr && out == nullptr) || (delta != nullptr && w_post == nullptr)) return PB_ERR_BAD_SIZE;
+    const int b = block_for(width);
+    if (dtype == PB_F32)
+        return launch_pdl(post_norm_add_bias_kernel<float>, dim3(n), dim3(b), 0, stream, residual, (const float*)delta, bias, w_post,
+                          eps_post, (float*)out, width);
+    if (dtype == PB_BF16)
+        return launch_pdl(post_norm_add_bias_kernel<__nv_bfloat16>, dim3(n), dim3(b), 0, stream, residual, (const __nv_bfloat16*)delta,
+                          bias, w_post, eps_post, (__nv_bfloat16*)out, width);
+    return PB_ERR_BAD_DTYPE;
+}
+
+// out [n, inter] (dtype) = gated(gate + bias[:inter], up + bias[inter:]) with gate_up [n, 2 inter] (in_dtype: float32 or
+// dtype); limit <= 0 means none.
+PB_EXPORT int pb_glu_bias(int in_dtype, int dtype, const void* gate_up, const float* bias, void* out, int n, int inter, float limit,
+                          float alpha, float shift, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (inter <= 0) return PB_ERR_BAD_SIZE;
+    const size_t total = (size_t)n * inter;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    const GatedInter p(inter, limit > 0.0f ? limit : __builtin_huge_valf(), alpha, shift);
+#define PB_GLU(TI, T) return launch_pdl(glu_bias_kernel<TI, T>, dim3((unsigned)blocks), dim3(256), 0, stream, (const TI*)gate_up, bias, \
+                                        (T*)out, total, p)
+    if (in_dtype == PB_F32 && dtype == PB_F32) PB_GLU(float, float);
+    if (in_dtype == PB_F32 && dtype == PB_BF16) PB_GLU(float, __nv_bfloat16);
+    if (in_dtype == PB_BF16 && dtype == PB_BF16) PB_GLU(__nv_bfloat16, __nv_bfloat16);
+#undef PB_GLU
+    return PB_ERR_BAD_DTYPE;
 }

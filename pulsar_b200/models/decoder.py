@@ -110,6 +110,7 @@ class DecoderModel(Part):
         for i, call in enumerate(s.run_order):
             following = self.blocks[s.run_order[i + 1].block] if i + 1 < len(s.run_order) else None
             ctx.next_norm = getattr(following, "mixer_norm", None)
+            ctx.has_following = following is not None
             delta = self.blocks[call.block].forward(ctx, residual, delta, ctx.cache(call.cache))
             if ctx.on_layer is not None:
                 ctx.on_layer(i, residual, delta)

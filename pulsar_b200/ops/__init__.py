@@ -84,12 +84,12 @@ _SIGNATURES = {
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P],
     "pb_sample_workspace": [_I],
     "pb_argmax": [_P, _I, _I, _P, _P, _P],
-    "pb_paged_attention_general": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "pb_paged_attention_general": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
     "pb_attention_general_tiled_supported": [_I, _P, _P, _I, _I, _I, _I, _I, _I],
-    "pb_paged_attention_general_tiled": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "pb_paged_attention_general_tiled": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
     "pb_attention_general_tc_tile": [],
     "pb_attention_general_tc_supported": [_I, _P, _P, _P, _I, _I, _I, _I, _I, _I],
-    "pb_paged_attention_general_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "pb_paged_attention_general_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
     "pb_qkv_split_write": [_I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "pb_heads_linear": [_I, _I, _P, _L, _I, _P, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P],
     "pb_latent_prepare": [_I, _P, _L, _P, _L, _P, _F, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -103,6 +103,14 @@ _SIGNATURES = {
     "pb_selective_scan_prompt": [_I, _P, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _I, _I, _I, _I, _P],
     "pb_post_norm_add": [_I, _P, _P, _P, _F, _P, _F, _P, _I, _I, _P],
     "pb_clamped_glu": [_I, _P, _P, _I, _I, _F, _F, _P],
+    "pb_post_norm_add_bias": [_I, _P, _P, _P, _P, _F, _P, _I, _I, _P],
+    "pb_glu_bias": [_I, _I, _P, _P, _P, _I, _I, _F, _F, _F, _P],
+    "pb_qk_prepare": [_I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "pb_sigmoid_gate_strided": [_I, _I, _P, _P, _L, _I, _I, _P],
+    "pb_add_bias": [_I, _P, _P, _I, _I, _P],
+    "pb_moe_route": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "pb_moe_gate_up": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _F, _P],
+    "pb_moe_down": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
 }
 _fns = {}
 # the entry points that launch kernels (the others answer questions on the host): what PULSAR_PROF=1 times
@@ -112,7 +120,8 @@ _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk
               "paged_attention_prefill_tc", "paged_attention_prefill_tcgen05", "gemm_skinny", "gemm_skinny_accumulate",
               "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update",
               "paged_attention_general", "paged_attention_general_tiled", "paged_attention_general_tc", "qkv_split_write", "heads_linear", "latent_prepare", "latent_expand_keys", "sigmoid_gate", "causal_conv_silu",
-              "selective_scan", "selective_scan_prompt", "selective_scan_chunked", "post_norm_add", "clamped_glu"}
+              "selective_scan", "selective_scan_prompt", "selective_scan_chunked", "post_norm_add", "clamped_glu",
+              "post_norm_add_bias", "glu_bias", "qk_prepare", "sigmoid_gate_strided", "add_bias", "moe_route", "moe_gate_up", "moe_down"}
 
 
 class KernelError(RuntimeError):
@@ -937,16 +946,21 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
                             block_table: torch.Tensor, scale: float, window: Optional[int] = None, chunk: Optional[int] = None,
                             slopes: Optional[torch.Tensor] = None, key_width: Optional[int] = None,
                             value_width: Optional[int] = None, tiled: Optional[bool] = None,
-                            tensor_cores: Optional[bool] = None) -> None:
+                            tensor_cores: Optional[bool] = None, keep_first: int = 0, softcap: Optional[float] = None,
+                            sinks: Optional[torch.Tensor] = None) -> None:
     """Attention of the step's tokens (``ctx``: cu_q, kv_len, seq_of_token, host.q_lens) with float32 queries ``q``
     [N, Hq, Dk] over pools [pages, Hkv, page, stride]: keys are the first ``key_width`` (default: all) elements of a
     ``k_pool`` row, values the first ``value_width`` of a ``v_pool`` row (the two may be one tensor).  ``slopes`` [Hq]
-    float32: the score loses slopes[h] * distance.  ``window`` / ``chunk`` bound the visible keys from below.
+    float32: the score loses slopes[h] * distance.  ``window`` / ``chunk`` bound the visible keys from below; the first
+    ``keep_first`` keys of a sequence stay visible all the same.  ``softcap``: the scaled score becomes softcap *
+    tanh(score / softcap).  ``sinks`` [Hq] float32: the softmax's denominator also holds exp(sinks[h]).
     ``tiled``: None picks the tiled kernel where it applies, False forces the plain one.  ``tensor_cores``: None picks the
     tensor-core kernel for steps with portions where it applies, False never, True insists."""
-    _cuda(q, k_pool, v_pool, out, block_table, slopes)
+    _cuda(q, k_pool, v_pool, out, block_table, slopes, sinks)
     _check_against(k_pool)
     n, hq, dk = q.shape
+    keep_first, softcap = int(keep_first or 0), float(softcap or 0.0)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == hq)
     pages, hkv, page_size, k_stride = k_pool.shape
     v_stride = v_pool.shape[3]
     dv = out.shape[2]
@@ -967,7 +981,8 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
             check(fn("pb_paged_attention_general_tc")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
                                                       block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len), _p(slopes), len(q_lens),
                                                       n_q_tiles, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale),
-                                                      int(window or 0), int(chunk or 0), stream()), "paged_attention_general_tc")
+                                                      int(window or 0), int(chunk or 0), keep_first, softcap, _p(sinks), stream()),
+                  "paged_attention_general_tc")
             return
         if insist:
             raise KernelError("paged_attention_general: the tensor-core kernel does not take these sizes or dtypes")
@@ -983,13 +998,13 @@ def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
                                                      _p(block_table), block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len),
                                                      _p(slopes), n, len(ctx.host.q_lens), row_tiles, n_splits, hq, hkv, dk, dv,
                                                      k_stride, v_stride, page_size, float(scale), int(window or 0),
-                                                     int(chunk or 0), stream()),
+                                                     int(chunk or 0), keep_first, softcap, _p(sinks), stream()),
               "paged_attention_general_tiled", kernels=2 if n_splits > 1 else 1)
         return
     check(fn("pb_paged_attention_general")(code(out.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
                                            block_table.shape[1], _p(ctx.cu_q), _p(ctx.kv_len), _p(ctx.seq_of_token), _p(slopes),
                                            n, hq, hkv, dk, dv, k_stride, v_stride, page_size, float(scale), int(window or 0),
-                                           int(chunk or 0), stream()), "paged_attention_general")
+                                           int(chunk or 0), keep_first, softcap, _p(sinks), stream()), "paged_attention_general")
 
 
 def qkv_split_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
@@ -1165,3 +1180,119 @@ def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: f
     assert two_i % 2 == 0 and out.shape == (n, two_i // 2) and out.dtype == gate_up.dtype
     check(fn("pb_clamped_glu")(code(out.dtype), _p(gate_up), _p(out), n, two_i // 2, float(limit), float(alpha), stream()),
           "clamped_glu")
+
+
+# ---------------------------------------------------------------- sublayers that read the stream itself; biases
+def post_norm_add_bias(residual: torch.Tensor, delta: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                       w_post: Optional[torch.Tensor], eps_post: float, out: Optional[torch.Tensor]) -> None:
+    """residual (float32) += rmsnorm(delta + bias) * w_post, and ``out`` = the stream as it now is, in the activation dtype
+    (for the sublayer that reads it next).  ``delta`` None: only ``out`` is written."""
+    _cuda(residual, delta, bias, w_post, out)
+    n, width = residual.shape
+    assert residual.dtype == torch.float32 and (delta is not None or out is not None)
+    dtype = delta.dtype if delta is not None else out.dtype
+    if delta is not None:
+        assert delta.shape == residual.shape and w_post.dtype == torch.float32 and w_post.numel() == width
+        assert bias is None or (bias.dtype == torch.float32 and bias.numel() == width)
+    assert out is None or (out.shape == residual.shape and out.dtype == dtype)
+    check(fn("pb_post_norm_add_bias")(code(dtype), _p(residual), _p(delta), _p(bias), _p(w_post), float(eps_post), _p(out), n, width,
+                                      stream()), "post_norm_add_bias")
+
+
+def glu_bias(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, gating=None) -> None:
+    """out [N, I] = the gated unit of ``gate_up`` [N, 2I] + ``bias`` [2I] (gate columns, then up columns): SwiGLU, or with
+    ``gating`` = (limit, alpha, shift) the clamped form of ``gated_linear``.  ``gate_up`` is float32 or of ``out``'s dtype."""
+    _cuda(gate_up, bias, out)
+    n, two_i = gate_up.shape
+    assert two_i % 2 == 0 and out.shape == (n, two_i // 2) and gate_up.dtype in (out.dtype, torch.float32)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == two_i)
+    limit, alpha, shift = gating if gating is not None else (0.0, 1.0, 0.0)
+    check(fn("pb_glu_bias")(code(gate_up.dtype), code(out.dtype), _p(gate_up), _p(bias), _p(out), n, two_i // 2, float(limit), float(alpha), float(shift),
+                            stream()), "glu_bias")
+
+
+def qk_prepare(rows: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+               slots: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], n_heads: int,
+               n_kv_heads: int, head_dim: int, rotary: int, page_size: int, q_bias: Optional[torch.Tensor] = None,
+               k_bias: Optional[torch.Tensor] = None, unit_norm_eps: Optional[float] = None, values_from_keys: bool = False) -> None:
+    """Per head of the projection rows ``rows`` [N, >= (Hq + Hkv) * D] (query heads, then key heads; float32 or the
+    pools' dtype; a column slice of a wider tensor will do): + bias; a key head as it then is goes to the value pool
+    (``values_from_keys``); the first ``rotary`` dimensions turn in the rotate-half layout by ``cos`` / ``sin``
+    [N, rotary / 2]; the head is divided by its root mean square (``unit_norm_eps``, no weight).  Queries to float32
+    ``q_out`` [N, Hq, D], keys into their pages.  ``n_kv_heads`` 0: queries only."""
+    _cuda(q_out, k_pool, v_pool, slots, cos, sin, q_bias, k_bias)
+    _check_against(k_pool)
+    n = rows.shape[0]
+    assert rows.is_cuda and rows.stride(1) == 1 and rows.shape[1] >= (n_heads + n_kv_heads) * head_dim
+    assert q_out.dtype == torch.float32 and q_out.shape == (n, n_heads, head_dim)
+    pool_dtype = k_pool.dtype if n_kv_heads else rows.dtype
+    if n_kv_heads:
+        assert slots.dtype == torch.int32 and k_pool.shape[1:] == (n_kv_heads, page_size, head_dim)
+        assert not values_from_keys or (v_pool.shape == k_pool.shape and v_pool.dtype == k_pool.dtype)
+    if rotary:
+        assert cos.dtype == torch.float32 and cos.shape == (n, rotary // 2) and sin.shape == cos.shape and sin.dtype == cos.dtype
+    for b, heads in ((q_bias, n_heads), (k_bias, n_kv_heads)):
+        assert b is None or (b.dtype == torch.float32 and b.numel() == heads * head_dim)
+    check(fn("pb_qk_prepare")(code(rows.dtype), code(pool_dtype), _p(rows), rows.stride(0), _p(q_bias), _p(k_bias), _p(cos), _p(sin),
+                              _p(q_out), _p(k_pool), _p(v_pool), _p(slots), n, n_heads, n_kv_heads, head_dim, int(rotary),
+                              -1.0 if unit_norm_eps is None else float(unit_norm_eps), 1 if values_from_keys else 0, page_size,
+                              stream()), "qk_prepare")
+
+
+def sigmoid_gate_strided(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x[n, :] *= sigmoid(gate[n, :]) in place (float32 arithmetic); ``gate`` float32 or of x's dtype, possibly a column slice."""
+    _cuda(x)
+    n, width = x.shape
+    assert gate.is_cuda and gate.shape == (n, width) and gate.stride(1) == 1
+    check(fn("pb_sigmoid_gate_strided")(code(x.dtype), code(gate.dtype), _p(x), _p(gate), gate.stride(0), n, width, stream()),
+          "sigmoid_gate_strided")
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """x [N, width] += bias [width] (float32) in place."""
+    _cuda(x, bias)
+    assert x.dim() == 2 and bias.dtype == torch.float32 and bias.numel() == x.shape[1]
+    check(fn("pb_add_bias")(code(x.dtype), _p(x), _p(bias), x.shape[0], x.shape[1], stream()), "add_bias")
+
+
+# ---------------------------------------------------------------- mixture of experts
+def moe_route(h: torch.Tensor, router: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, scale: float = 1.0,
+              renormalize: bool = False) -> None:
+    """ids [N, top] int32 and weights [N, top] float32 of the ``top`` largest sigmoid(router @ h) per token (float32 sums;
+    ties go to the lower index), weights times ``scale`` (after division by their sum with ``renormalize``)."""
+    _cuda(h, router, ids, weights)
+    n, width = h.shape
+    e = router.shape[0]
+    top = ids.shape[1]
+    assert router.dtype == torch.float32 and router.shape == (e, width) and ids.dtype == torch.int32 and ids.shape == (n, top)
+    assert weights.dtype == torch.float32 and weights.shape == (n, top)
+    check(fn("pb_moe_route")(code(h.dtype), _p(h), _p(router), _p(ids), _p(weights), n, width, e, top, float(scale),
+                             1 if renormalize else 0, stream()), "moe_route")
+
+
+def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor, act: torch.Tensor, gating) -> None:
+    """act [N * top, ff] = the gated unit (``gating`` = (limit, alpha, shift) as in ``gated_linear``; None: SwiGLU) of every
+    token's chosen experts; ``w_gate_up`` [E, 2 ff, width] holds an expert's gate rows, then its up rows."""
+    _cuda(h, w_gate_up, ids, act)
+    n, width = h.shape
+    e, two_ff, w2 = w_gate_up.shape
+    top = ids.shape[1]
+    assert w2 == width and two_ff % 2 == 0 and act.shape == (n * top, two_ff // 2) and h.dtype == w_gate_up.dtype == act.dtype
+    assert ids.dtype == torch.int32 and ids.shape[0] == n
+    limit, alpha, shift = gating if gating is not None else (0.0, 1.0, 0.0)
+    check(fn("pb_moe_gate_up")(code(h.dtype), _p(h), _p(w_gate_up), _p(ids), _p(act), n, width, two_ff // 2, top, float(limit),
+                               float(alpha), float(shift), stream()), "moe_gate_up")
+
+
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, add: Optional[torch.Tensor],
+             out: torch.Tensor) -> None:
+    """out [N, width] = add + sum over a token's chosen experts, in the order of ``ids``, of weight * (w_down[e] @ act row)."""
+    _cuda(act, w_down, ids, weights, add, out)
+    n, width = out.shape
+    e, w2, ff = w_down.shape
+    top = ids.shape[1]
+    assert w2 == width and act.shape == (n * top, ff) and act.dtype == w_down.dtype == out.dtype
+    assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.shape == weights.shape == (n, top)
+    assert add is None or (add.shape == out.shape and add.dtype == out.dtype)
+    check(fn("pb_moe_down")(code(out.dtype), _p(act), _p(w_down), _p(ids), _p(weights), _p(add), _p(out), n, width, ff, top, stream()),
+          "moe_down")

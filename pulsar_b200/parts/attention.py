@@ -28,17 +28,45 @@ class Attention(Mixer):
     linear distance bias per head) has no rotation and no per-head norm; positions enter through the bias and
     the masks alone.  Its queries stay float32 from the projection to the scores
     (``ops.qkv_split_write`` / ``ops.paged_attention_general``).
+
+    The general form also carries what further designs ask of an attention layer, each a field of the specification:
+    biases of the projections, values that are the projected keys (no v projection), rotation in the rotate-half layout
+    followed by a division of q and k by their root mean square (``qk_norm_weight`` False, ``qk_norm_after_rotation``),
+    a cap on the scaled scores, first keys that stay visible below a window (``keep_first``), a learned sink per head in
+    the softmax's denominator, and a sigmoid gate on the concatenated heads from a projection of the mixer's input.
+    With any of these the fused projection (rows q | k | v | gate) is a float32 product, the bias is added in float32,
+    and ``ops.qk_prepare`` does what stands between it and the attention kernels.
+
+    ``output_bias`` is the output projection's bias (or None).  ``forward`` adds it unless the block has set
+    ``defer_output_bias`` because the kernel behind the mixer takes it along.
     """
+
+    output_bias: Optional[torch.Tensor] = None
+    defer_output_bias: bool = False
 
     def __init__(self, spec: MixerSpec, prefix: str, dtype: torch.dtype):
         if spec.n_heads <= 0 or spec.n_kv_heads <= 0 or spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"attention: {spec.n_heads} query heads cannot be grouped over {spec.n_kv_heads} kv heads")
-        self.general = bool(spec.value_dim != spec.head_dim or spec.chunk is not None or spec.distance_bias is not None)
+        # what only ops.qk_prepare does between the projection and the attention kernels (its rows may be wider than
+        # q | k, so the gate's columns ride along in the same product)
+        self.prepared = bool(spec.bias or spec.values_from_keys or not spec.qk_norm_weight or spec.qk_norm_after_rotation
+                             or spec.output_gate)
+        self.general = bool(spec.value_dim != spec.head_dim or spec.chunk is not None or spec.distance_bias is not None
+                            or spec.keep_first or spec.softcap is not None or spec.sinks or spec.output_gate or self.prepared)
         if self.general:
-            if spec.position is not None or spec.qk_norm_eps is not None:
+            if not self.prepared and (spec.position is not None or spec.qk_norm_eps is not None):
                 raise ValueError("attention: the general form (value width, chunk mask, distance bias) has neither rotation nor q/k norm")
+            if self.prepared:
+                if spec.qk_norm_eps is not None and (spec.qk_norm_weight or not spec.qk_norm_after_rotation):
+                    raise ValueError("attention: with biases or values from keys the q/k norm is the one without a weight, behind the rotation")
+                if spec.own_kv and not spec.values_from_keys:
+                    raise ValueError("attention: biases and the weightless q/k norm are implemented for values that are the keys")
+                if spec.values_from_keys and spec.value_dim != spec.head_dim:
+                    raise ValueError("attention: values that are the keys are as wide as the keys")
             if spec.head_dim <= 0 or spec.value_dim <= 0 or (spec.chunk is not None and spec.chunk <= 0):
                 raise ValueError("attention: head sizes and the chunk size must be positive")
+            if spec.keep_first < 0 or (spec.softcap is not None and not (spec.softcap > 0.0)):
+                raise ValueError("attention: keep_first must not be negative and the cap on the scores must be positive")
         elif spec.head_dim % 16 or spec.head_dim > 256:
             raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16, at most 256")
         if spec.window is not None and spec.window <= 0:
@@ -46,20 +74,37 @@ class Attention(Mixer):
         self.spec, self.prefix, self.dtype = spec, prefix, dtype
         self.position = POSITIONS.get(spec.position.kind)(spec.position) if spec.position is not None else None
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.slopes = None
+        self.q_bias = self.k_bias = self.sinks = None
         name = spec.tensor_name
         self.names = {"q": name("q", "q_proj.weight"), "k": name("k", "k_proj.weight"), "v": name("v", "v_proj.weight"),
                       "o": name("o", "o_proj.weight"), "q_norm": name("q_norm", "q_norm.weight"),
-                      "k_norm": name("k_norm", "k_norm.weight")}
+                      "k_norm": name("k_norm", "k_norm.weight"), "gate": name("gate", "g_proj.weight"),
+                      "sinks": name("sinks", "sinks")}
+        for role in ("q", "k", "o"):          # a bias is named after its weight unless the specification names it
+            weight = self.names[role]
+            default = weight[:-len(".weight")] + ".bias" if weight.endswith(".weight") else weight + ".b"
+            self.names[role + "_bias"] = name(role + "_bias", default)
+        self.own_v = spec.own_kv and not spec.values_from_keys
 
     # ---------------------------------------------------------------- weights
     def weight_specs(self) -> List[WeightSpec]:
         s, p, nm = self.spec, self.prefix, self.names
         specs = [WeightSpec(p + nm["q"], (s.n_heads * s.head_dim, s.hidden))]
         if s.own_kv:
-            specs += [WeightSpec(p + nm["k"], (s.n_kv_heads * s.head_dim, s.hidden)),
-                      WeightSpec(p + nm["v"], (s.n_kv_heads * s.value_dim, s.hidden))]
+            specs.append(WeightSpec(p + nm["k"], (s.n_kv_heads * s.head_dim, s.hidden)))
+        if self.own_v:
+            specs.append(WeightSpec(p + nm["v"], (s.n_kv_heads * s.value_dim, s.hidden)))
+        if s.output_gate:
+            specs.append(WeightSpec(p + nm["gate"], (s.n_heads * s.value_dim, s.hidden)))
         specs.append(WeightSpec(p + nm["o"], (s.hidden, s.n_heads * s.value_dim)))
-        if s.qk_norm_eps is not None:
+        if s.bias:
+            specs.append(WeightSpec(p + nm["q_bias"], (s.n_heads * s.head_dim,), role="vector", init="small"))
+            if s.own_kv:
+                specs.append(WeightSpec(p + nm["k_bias"], (s.n_kv_heads * s.head_dim,), role="vector", init="small"))
+            specs.append(WeightSpec(p + nm["o_bias"], (s.hidden,), role="vector", init="small"))
+        if s.sinks:
+            specs.append(WeightSpec(p + nm["sinks"], (s.n_heads,), role="vector", init="small"))
+        if s.qk_norm_eps is not None and s.qk_norm_weight:
             specs.append(WeightSpec(p + nm["q_norm"], (s.head_dim,), role="vector", init="ones_normal"))
             if s.own_kv:
                 specs.append(WeightSpec(p + nm["k_norm"], (s.head_dim,), role="vector", init="ones_normal"))
@@ -69,10 +114,19 @@ class Attention(Mixer):
         s, p, nm = self.spec, self.prefix, self.names
         parts = [tensors[p + nm["q"]]]
         if s.own_kv:
-            parts += [tensors[p + nm["k"]], tensors[p + nm["v"]]]
-        self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0]   # rows: q | k | v
+            parts.append(tensors[p + nm["k"]])
+        if self.own_v:
+            parts.append(tensors[p + nm["v"]])
+        if s.output_gate:
+            parts.append(tensors[p + nm["gate"]])
+        self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0]   # rows: q | k | v | gate
         self.w_o = tensors[p + nm["o"]]
-        if s.qk_norm_eps is not None:
+        if s.bias:
+            self.q_bias, self.k_bias = tensors[p + nm["q_bias"]], tensors.get(p + nm["k_bias"])
+            self.output_bias = tensors[p + nm["o_bias"]]
+        if s.sinks:
+            self.sinks = tensors[p + nm["sinks"]]
+        if s.qk_norm_eps is not None and s.qk_norm_weight:
             self.q_norm = tensors[p + nm["q_norm"]]
             self.k_norm = tensors.get(p + nm["k_norm"])
         if s.distance_bias is not None:
@@ -80,26 +134,37 @@ class Attention(Mixer):
             self.slopes = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(self.w_o.device)
 
     def weight_bytes(self) -> int:
-        ts = [self.w_qkv, self.w_o, self.q_norm, self.k_norm, self.slopes]
+        ts = [self.w_qkv, self.w_o, self.q_norm, self.k_norm, self.slopes, self.q_bias, self.k_bias, self.output_bias, self.sinks]
         return sum(t.numel() * t.element_size() for t in ts if t is not None)
 
     def cache_need(self) -> CacheNeed:
         s = self.spec
+        # Pages behind a window go back to the pool as the queries pass them; with kept first keys every page stays
+        # (the kept keys' pages are needed for good, and the manager releases from the front only).
+        window = None if s.keep_first else s.window
         if s.value_dim != s.head_dim:
             return CacheNeed.paged((CachedTensor("k", s.n_kv_heads, s.head_dim), CachedTensor("v", s.n_kv_heads, s.value_dim)),
-                                   s.window)
-        return CacheNeed.paged_kv(s.n_kv_heads, s.head_dim, s.window)
+                                   window)
+        return CacheNeed.paged_kv(s.n_kv_heads, s.head_dim, window)
 
     # ---------------------------------------------------------------- one step
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: CacheView) -> torch.Tensor:
         s = self.spec
         n = ctx.n_tokens
-        n_kv = s.n_kv_heads if s.own_kv else 0
-        qkv = ctx.scratch("attn.qkv", (n, s.n_heads * s.head_dim + n_kv * (s.head_dim + s.value_dim)))
+        if self.prepared:
+            # float32 rows: the biases join before anything is rounded, and the queries are float32 from here on anyway
+            qkv = ctx.scratch("attn.qkv32", (n, self.w_qkv.shape[0]), torch.float32)
+        else:
+            qkv = ctx.scratch("attn.qkv", (n, self.w_qkv.shape[0]))
         ops.linear(h, self.w_qkv, qkv)
         o = self._attend_general(ctx, qkv, cache) if self.general else self._attend(ctx, qkv, cache)
+        if s.output_gate:
+            at = self.w_qkv.shape[0] - s.n_heads * s.value_dim
+            ops.sigmoid_gate_strided(o.view(n, s.n_heads * s.value_dim), qkv[:, at:])
         out = ctx.scratch("attn.out", (n, s.hidden))
         ops.linear(o.view(n, s.n_heads * s.value_dim), self.w_o, out)
+        if self.output_bias is not None and not self.defer_output_bias:
+            ops.add_bias(out, self.output_bias)
         return out
 
     def _attend_general(self, ctx: StepContext, qkv: torch.Tensor, cache: CacheView) -> torch.Tensor:
@@ -108,11 +173,21 @@ class Attention(Mixer):
         n = ctx.n_tokens
         n_kv = s.n_kv_heads if s.own_kv else 0
         q = ctx.scratch("attn.q32", (n, s.n_heads, s.head_dim), torch.float32)
-        ops.qkv_split_write(qkv, q, cache.k_pool if n_kv else None, cache.v_pool if n_kv else None,
-                            cache.slots if n_kv else None, s.n_heads, n_kv, s.head_dim, s.value_dim, cache.page_size)
+        if self.prepared:
+            cos = sin = None
+            rotary = 0
+            if self.position is not None:
+                cos, sin = self.position.tables(ctx)
+                rotary = s.position.rotary_dim
+            ops.qk_prepare(qkv, q, cache.k_pool if n_kv else None, cache.v_pool if n_kv else None, cache.slots if n_kv else None,
+                           cos, sin, s.n_heads, n_kv, s.head_dim, rotary, cache.page_size, self.q_bias, self.k_bias if n_kv else None,
+                           s.qk_norm_eps, s.values_from_keys)
+        else:
+            ops.qkv_split_write(qkv, q, cache.k_pool if n_kv else None, cache.v_pool if n_kv else None,
+                                cache.slots if n_kv else None, s.n_heads, n_kv, s.head_dim, s.value_dim, cache.page_size)
         o = ctx.scratch("attn.o", (n, s.n_heads, s.value_dim))
         ops.paged_attention_general(ctx, q, cache.k_pool, cache.v_pool, o, cache.block_table, s.scale, s.window, s.chunk,
-                                    self.slopes)
+                                    self.slopes, keep_first=s.keep_first, softcap=s.softcap, sinks=self.sinks)
         return o
 
     def forward_normed(self, ctx: StepContext, residual: torch.Tensor, norm, cache: CacheView, next_norm=None) -> bool:

@@ -87,6 +87,7 @@ class StepContext:
         # the activation dtype, parts of the rows' sums of squares).  Valid while nothing else touches the residual.
         self.prepared_norms: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self.next_norm = None                   # the first norm of the block that runs after the current one, if known
+        self.has_following = True               # False while the last entry of the run order runs
         # A norm that was already applied to the residual as it stands, by that norm's id: the normalised rows in the
         # activation dtype.  Valid while nothing else touches the residual.
         self.normed: Dict[int, torch.Tensor] = {}

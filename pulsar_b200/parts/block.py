@@ -118,3 +118,85 @@ class SandwichBlock(Block):
         else:
             ops.post_norm_add(residual, out, post.weight, post.spec.eps)
         return None
+
+
+@BLOCKS.register("postnorm")
+class PostNormBlock(Block):
+    """x += post1(mixer(x)); x += post2(feed_forward(x)): the sublayers read the stream itself and only their outputs are
+    normed (RMS norms; the specification's ``mixer_post_norm`` / ``feed_forward_post_norm``).  A block without a
+    feed-forward has the first sublayer only.
+
+    The stream is float32 and complete when the block returns.  One kernel stands behind every sublayer
+    (``ops.post_norm_add_bias``): it adds the bias of the sublayer's last projection (where it has one and defers it),
+    norms, adds into the stream and leaves the stream's rounding to the activation dtype for the sublayer that reads it
+    next (``ctx.normed["stream"]``; a float32 engine reads the stream itself)."""
+
+    def __init__(self, spec: BlockSpec, dtype: torch.dtype):
+        self.spec, self.dtype = spec, dtype
+
+        def norm(norm_spec, part, tag):
+            made = NORMS.get(norm_spec.kind)(norm_spec, spec.sub_prefix(part), dtype, tag)
+            if not isinstance(made, RMSNorm):
+                raise ValueError(f"a postnorm block's norms are RMS norms, '{norm_spec.kind}' is not")
+            return made
+        if spec.mixer_post_norm is None:
+            raise ValueError("a postnorm block needs a norm behind its mixer")
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, spec.sub_prefix("mixer"), dtype)
+        self.mixer_post_norm = norm(spec.mixer_post_norm, "mixer_post_norm", "norm.mixer.post")
+        self.feed_forward = self.feed_forward_post_norm = None
+        if spec.feed_forward is not None:
+            if spec.feed_forward_post_norm is None:
+                raise ValueError("a postnorm block with a feed-forward needs the norm behind it")
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, spec.sub_prefix("feed_forward"), dtype)
+            self.feed_forward_post_norm = norm(spec.feed_forward_post_norm, "feed_forward_post_norm", "norm.ffn.post")
+        for part in (self.mixer, self.feed_forward):
+            if part is not None and hasattr(part, "defer_output_bias"):
+                part.defer_output_bias = True          # the kernel behind the sublayer adds it
+        self.parts = tuple(p for p in (self.mixer, self.mixer_post_norm, self.feed_forward, self.feed_forward_post_norm)
+                           if p is not None)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [w for p in self.parts for w in p.weight_specs()]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts:
+            p.load(tensors)
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in self.parts)
+
+    def _reader(self, ctx: StepContext, residual: torch.Tensor, fresh: bool) -> Optional[torch.Tensor]:
+        """Where the kernel behind a sublayer leaves the stream for the next reader (None: the reader takes the float32
+        stream itself); ``fresh`` also fills it from the stream as it stands."""
+        if self.dtype == torch.float32:
+            return None
+        h = ctx.scratch("stream.rounded", residual.shape)
+        if fresh:
+            ops.post_norm_add_bias(residual, None, None, None, 0.0, h)
+        return h
+
+    def forward(self, ctx: StepContext, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                cache: CacheView) -> Optional[torch.Tensor]:
+        ctx.prepared_norms.clear()
+        if delta is not None:
+            raise ValueError("a postnorm block follows blocks that leave the stream complete")
+        h = ctx.normed.pop("stream", None)
+        ctx.normed.clear()
+        if self.dtype == torch.float32:
+            h = residual
+        elif h is None:
+            h = self._reader(ctx, residual, fresh=True)
+        out = self.mixer.forward(ctx, h, cache)
+        post = self.mixer_post_norm
+        bias = getattr(self.mixer, "output_bias", None)
+        if self.feed_forward is not None:
+            nxt = self._reader(ctx, residual, fresh=False)
+            ops.post_norm_add_bias(residual, out, bias, post.weight, post.spec.eps, nxt)
+            out = self.feed_forward.forward(ctx, residual if nxt is None else nxt)
+            post = self.feed_forward_post_norm
+            bias = getattr(self.feed_forward, "output_bias", None)
+        nxt = self._reader(ctx, residual, fresh=False) if ctx.has_following else None
+        ops.post_norm_add_bias(residual, out, bias, post.weight, post.spec.eps, nxt)
+        if nxt is not None:
+            ctx.normed["stream"] = nxt
+        return None

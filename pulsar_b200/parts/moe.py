@@ -1,0 +1,88 @@
+"""A mixture of gated experts with a sigmoid router and an optional shared expert."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from ..config.registry import FEED_FORWARDS
+from ..config.specs import FeedForwardSpec
+from .base import FeedForward, StepContext, WeightSpec
+
+
+@FEED_FORWARDS.register("moe")
+class MixtureOfExperts(FeedForward):
+    """Every token is sent to the ``top`` experts with the largest router scores s = sigmoid(W_r h) (float32 logits) and
+    receives sum over them of w_e * expert_e(h), with w_e = s_e * ``router_scale`` (divided by the chosen scores' sum
+    first where ``renormalize`` is set).  An expert is a clamped gated unit without biases,
+    W_down (g' * sigmoid(alpha g') * (u' + shift)), g' = min(W_gate h, limit), u' = clamp(W_up h, -limit, limit);
+    ``spec.intermediate`` is an expert's inner width.  A shared expert (a feed-forward specification of its own under
+    the option ``shared``) runs for every token and is added.
+
+    Options (``spec.extra``): ``experts``, ``top``, ``router_scale``, ``renormalize``, ``limit``, ``alpha``, ``shift``,
+    ``shared`` (FeedForwardSpec or None), ``shared_prefix`` ("shared."), ``tensor_names`` by role "router", "gate", "up",
+    "down" (an expert's tensors are ``<prefix>e<i>.<name>``).
+
+    The router's choice stays on the device: the kernels take the chosen ids as an array, so a step of single tokens can
+    be captured into a CUDA graph.  Steps of a few tokens read each chosen expert's weights per token
+    (``ops.moe_gate_up`` / ``ops.moe_down``: a warp per output element, fixed order of addition)."""
+
+    def __init__(self, spec: FeedForwardSpec, prefix: str, dtype: torch.dtype):
+        self.spec, self.prefix, self.dtype = spec, prefix, dtype
+        self.n_experts, self.top = int(spec.option("experts", 0)), int(spec.option("top", 0))
+        if not (0 < self.top <= self.n_experts):
+            raise ValueError(f"moe: top ({self.top}) must lie between 1 and the number of experts ({self.n_experts})")
+        self.router_scale = float(spec.option("router_scale", 1.0))
+        self.renormalize = bool(spec.option("renormalize", False))
+        limit = spec.option("limit", None)
+        self.gating = (float(limit) if limit else 0.0, float(spec.option("alpha", 1.702)), float(spec.option("shift", 1.0)))
+        names = dict(spec.option("tensor_names", ()))
+        self.names = {r: names.get(r, d) for r, d in (("router", "router"), ("gate", "gate"), ("up", "up"), ("down", "down"))}
+        shared = spec.option("shared", None)
+        self.shared = None
+        if shared is not None:
+            self.shared = FEED_FORWARDS.get(shared.kind)(shared, prefix + str(spec.option("shared_prefix", "shared.")), dtype)
+        self.router = self.w_gate_up = self.w_down = None
+
+    def _expert(self, i: int, role: str) -> str:
+        return f"{self.prefix}e{i}.{self.names[role]}"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        s = self.spec
+        specs = []
+        for i in range(self.n_experts):
+            specs += [WeightSpec(self._expert(i, "gate"), (s.intermediate, s.hidden)),
+                      WeightSpec(self._expert(i, "up"), (s.intermediate, s.hidden)),
+                      WeightSpec(self._expert(i, "down"), (s.hidden, s.intermediate))]
+        specs.append(WeightSpec(self.prefix + self.names["router"], (self.n_experts, s.hidden), role="vector", init="normal"))
+        if self.shared is not None:
+            specs += self.shared.weight_specs()
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self.n_experts
+        self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]], dim=0)
+                                      for i in range(n)]).contiguous()                      # [E, 2 ff, width]
+        self.w_down = torch.stack([tensors[self._expert(i, "down")] for i in range(n)]).contiguous()    # [E, width, ff]
+        self.router = tensors[self.prefix + self.names["router"]].contiguous()
+        if self.shared is not None:
+            self.shared.load(tensors)
+
+    def weight_bytes(self) -> int:
+        """Bytes a step of one token reads: the router, the chosen experts, the shared expert."""
+        per_expert = (self.w_gate_up.numel() + self.w_down.numel()) // self.n_experts * self.w_down.element_size()
+        own = self.router.numel() * self.router.element_size() + self.top * per_expert
+        return own + (self.shared.weight_bytes() if self.shared is not None else 0)
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        s, n, top = self.spec, ctx.n_tokens, self.top
+        ids = ctx.scratch("moe.ids", (n, top), torch.int32)
+        weights = ctx.scratch("moe.weights", (n, top), torch.float32)
+        ops.moe_route(h, self.router, ids, weights, self.router_scale, self.renormalize)
+        shared = self.shared.forward(ctx, h) if self.shared is not None else None
+        act = ctx.scratch("moe.act", (n * top, s.intermediate))
+        ops.moe_gate_up(h, self.w_gate_up, ids, act, self.gating)
+        out = ctx.scratch("moe.out", (n, s.hidden))
+        ops.moe_down(act, self.w_down, ids, weights, shared, out)
+        return out
