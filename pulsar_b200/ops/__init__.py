@@ -111,6 +111,9 @@ _SIGNATURES = {
     "pb_moe_route": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "pb_moe_gate_up": [_I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _F, _P],
     "pb_moe_down": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "pb_moe_grouped_workspace": [_I, _I, _I],
+    "pb_moe_grouped_supported": [_I, _I, _I],
+    "pb_moe_grouped": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
 }
 _fns = {}
 # the entry points that launch kernels (the others answer questions on the host): what PULSAR_PROF=1 times
@@ -121,7 +124,7 @@ _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk
               "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update",
               "paged_attention_general", "paged_attention_general_tiled", "paged_attention_general_tc", "qkv_split_write", "heads_linear", "latent_prepare", "latent_expand_keys", "sigmoid_gate", "causal_conv_silu",
               "selective_scan", "selective_scan_prompt", "selective_scan_chunked", "post_norm_add", "clamped_glu",
-              "post_norm_add_bias", "glu_bias", "qk_prepare", "sigmoid_gate_strided", "add_bias", "moe_route", "moe_gate_up", "moe_down"}
+              "post_norm_add_bias", "glu_bias", "qk_prepare", "sigmoid_gate_strided", "add_bias", "moe_route", "moe_gate_up", "moe_down", "moe_grouped"}
 
 
 class KernelError(RuntimeError):
@@ -1296,3 +1299,38 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights
     assert add is None or (add.shape == out.shape and add.dtype == out.dtype)
     check(fn("pb_moe_down")(code(out.dtype), _p(act), _p(w_down), _p(ids), _p(weights), _p(add), _p(out), n, width, ff, top, stream()),
           "moe_down")
+
+
+# Steps of more than MOE_GROUPED_MIN tokens (bfloat16) sort their (token, expert) pairs by expert on the device and run every
+# expert's rows through tensor-core tiles; fewer tokens read each chosen expert's weights per token.  PULSAR_MOE_GROUPED=0
+# leaves the grouped products out.
+MOE_GROUPED = os.environ.get("PULSAR_MOE_GROUPED", "1") != "0"
+MOE_GROUPED_MIN = 16
+
+
+def moe_grouped_supported(dtype: torch.dtype, width: int, ff: int, n_experts: int) -> bool:
+    return bool(MOE_GROUPED and dtype == torch.bfloat16 and fn("pb_moe_grouped_supported")(width, ff, n_experts))
+
+
+def moe_grouped_workspace(n: int, top: int, n_experts: int) -> int:
+    """int32 elements of the workspace ``moe_grouped`` needs for ``n`` tokens."""
+    return int(fn("pb_moe_grouped_workspace")(n, top, n_experts))
+
+
+def moe_grouped(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                add: Optional[torch.Tensor], act: torch.Tensor, y: torch.Tensor, out: torch.Tensor, work: torch.Tensor, gating) -> None:
+    """What ``moe_gate_up`` and ``moe_down`` compute together, for steps of many tokens (bfloat16): pairs sorted by expert, the
+    experts' products in tensor-core tiles, the weighted sum in the order of ``ids``.  ``act`` [N * top, ff] bfloat16, ``y``
+    [N * top, width] float32 and ``work`` (int32, ``moe_grouped_workspace`` elements) are scratch."""
+    _cuda(h, w_gate_up, w_down, ids, weights, add, act, y, out, work)
+    n, width = h.shape
+    e, two_ff, w2 = w_gate_up.shape
+    ff, top = two_ff // 2, ids.shape[1]
+    assert h.dtype == w_gate_up.dtype == w_down.dtype == act.dtype == out.dtype == torch.bfloat16 and w2 == width
+    assert w_down.shape == (e, width, ff) and ids.dtype == torch.int32 and ids.shape == weights.shape == (n, top)
+    assert weights.dtype == torch.float32 and act.shape == (n * top, ff) and y.dtype == torch.float32 and y.shape == (n * top, width)
+    assert out.shape == (n, width) and (add is None or (add.shape == out.shape and add.dtype == out.dtype))
+    assert work.dtype == torch.int32 and work.numel() >= moe_grouped_workspace(n, top, e)
+    limit, alpha, shift = gating if gating is not None else (0.0, 1.0, 0.0)
+    check(fn("pb_moe_grouped")(_p(h), _p(w_gate_up), _p(w_down), _p(ids), _p(weights), _p(add), _p(act), _p(y), _p(out), _p(work), n,
+                               width, ff, e, top, float(limit), float(alpha), float(shift), stream()), "moe_grouped", kernels=4)

@@ -26,7 +26,9 @@ class MixtureOfExperts(FeedForward):
 
     The router's choice stays on the device: the kernels take the chosen ids as an array, so a step of single tokens can
     be captured into a CUDA graph.  Steps of a few tokens read each chosen expert's weights per token
-    (``ops.moe_gate_up`` / ``ops.moe_down``: a warp per output element, fixed order of addition)."""
+    (``ops.moe_gate_up`` / ``ops.moe_down``: a warp per output element, fixed order of addition); larger steps in bfloat16
+    sort the (token, expert) pairs by expert on the device and run each expert's rows through tensor-core tiles
+    (``ops.moe_grouped``)."""
 
     def __init__(self, spec: FeedForwardSpec, prefix: str, dtype: torch.dtype):
         self.spec, self.prefix, self.dtype = spec, prefix, dtype
@@ -82,7 +84,12 @@ class MixtureOfExperts(FeedForward):
         ops.moe_route(h, self.router, ids, weights, self.router_scale, self.renormalize)
         shared = self.shared.forward(ctx, h) if self.shared is not None else None
         act = ctx.scratch("moe.act", (n * top, s.intermediate))
-        ops.moe_gate_up(h, self.w_gate_up, ids, act, self.gating)
         out = ctx.scratch("moe.out", (n, s.hidden))
+        if n > ops.MOE_GROUPED_MIN and ops.moe_grouped_supported(h.dtype, s.hidden, s.intermediate, self.n_experts):
+            y = ctx.scratch("moe.y", (n * top, s.hidden), torch.float32)
+            work = ctx.scratch("moe.work", (ops.moe_grouped_workspace(n, top, self.n_experts),), torch.int32)
+            ops.moe_grouped(h, self.w_gate_up, self.w_down, ids, weights, shared, act, y, out, work, self.gating)
+            return out
+        ops.moe_gate_up(h, self.w_gate_up, ids, act, self.gating)
         ops.moe_down(act, self.w_down, ids, weights, shared, out)
         return out

@@ -122,9 +122,22 @@ def routed(h: torch.Tensor, router: torch.Tensor, top: int, scale: float):
     return idx, val * scale
 
 
-def moe_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], mlp: dict) -> torch.Tensor:
+def route_margins(h: torch.Tensor, router: torch.Tensor, top: int) -> torch.Tensor:
+    """[L]: how far the router's logits of the last chosen and the first rejected expert lie apart, relative to the
+    largest logit's magnitude (infinite where every expert is chosen).  A small margin is a close call: rounding may
+    choose otherwise."""
+    z = h @ router.T
+    if top >= z.shape[1]:
+        return torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    ordered = torch.sort(z, dim=-1, descending=True).values
+    return (ordered[:, top - 1] - ordered[:, top]) / z.abs().max(dim=-1).values.clamp_min(1e-30)
+
+
+def moe_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], mlp: dict, margins: Optional[list] = None) -> torch.Tensor:
     r, e = mlp["router"], mlp["expert"]
     idx, weight = routed(h, w["router"], int(r["top"]), float(r["scale"]))
+    if margins is not None:
+        margins.append(route_margins(h, w["router"], int(r["top"])))
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for c in range(idx.shape[1]):
@@ -141,8 +154,9 @@ def sub(weights: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64,
-            streams: Optional[list] = None) -> torch.Tensor:
-    """Logits [L, vocab] of one whole sequence.  ``streams``: a list that receives the stream after every layer."""
+            streams: Optional[list] = None, margins: Optional[list] = None) -> torch.Tensor:
+    """Logits [L, vocab] of one whole sequence.  ``streams``: a list that receives the stream after every layer;
+    ``margins``: a list that receives every routed layer's ``route_margins``."""
     w = {n: t.to(dtype) for n, t in weights.items()}
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][torch.tensor(list(tokens))]
@@ -153,7 +167,7 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
         x = x + rms_norm(attention(x, sub(w, p + "mix."), layer["mixer"], eps), w[p + "norm1"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            ff = dense_ff(x, sub(w, p + "mlp.")) if mlp["kind"] == "dense" else moe_ff(x, sub(w, p + "mlp."), mlp)
+            ff = dense_ff(x, sub(w, p + "mlp.")) if mlp["kind"] == "dense" else moe_ff(x, sub(w, p + "mlp."), mlp, margins)
             x = x + rms_norm(ff, w[p + "norm2"], eps)
         if streams is not None:
             streams.append(x.clone())
