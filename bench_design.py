@@ -45,8 +45,30 @@ def bubotar_config(z: dict) -> dict:
     return dict(architecture="Bubotar", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), logit_scale=1.0, layers=layers)
 
 
+# Topunex at sizes that resemble layers of real models: grouped attention with a window of 1,024 tokens below which the
+# first 4 keys stay visible, half of each head rotating; the first layer's feed-forward dense, the others 32 experts of
+# which a token uses 4, beside a shared expert.
+TOPUNEX_SIZES = {
+    "2k": dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, rot=64, window=1024, keep=4, ff=8192, experts=32, top=4,
+               expert_ff=1024, shared_ff=2048, vocab=32000),
+    "4k": dict(width=4096, layers=8, heads=32, kv_heads=8, dim=128, rot=64, window=1024, keep=4, ff=12288, experts=32, top=4,
+               expert_ff=2048, shared_ff=4096, vocab=32000),
+}
+
+
+def topunex_config(z: dict) -> dict:
+    mixer = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=1.0 / math.sqrt(z["dim"]), softcap=30.0,
+                 mask=dict(size=z["window"], keep_first=z["keep"]),
+                 rot=dict(base=500000.0, dims=z["rot"], scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), router=dict(experts=z["experts"], top=z["top"], scale=1.0),
+               shared=dict(ff=z["shared_ff"], limit=7.0))
+    layers = [dict(type="attention", mixer=dict(mixer), mlp=dict(kind="dense", ff=z["ff"]) if i == 0 else dict(moe))
+              for i in range(z["layers"])]
+    return dict(architecture="Topunex", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), layers=layers)
+
+
 def dense_config(z: dict) -> dict:
-    n = 4 * z["groups"]
+    n = z["layers"] if "layers" in z else 4 * z["groups"]
     return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=z["vocab"], hidden_size=z["width"],
                 intermediate_size=z["ff"], num_hidden_layers=n, num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
                 head_dim=z["dim"], rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=False,
@@ -169,10 +191,49 @@ def own_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
     return {k: (b * steps, f * steps, on) for k, (b, f, on) in work.items()}
 
 
+def _window_pairs(n_new: int, start: int, window: int, keep: int) -> float:
+    """(query, visible key) pairs of n_new tokens behind `start` cached ones under a window with kept first keys."""
+    total = 0.0
+    for p in range(start, start + n_new):
+        lo = max(0, p - window + 1)
+        total += p - lo + 1 + min(keep, lo)
+    return total
+
+
+def topunex_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
+    """Per kernel class of Topunex: (bytes it must move, flops, what the flops run on) summed over the layers of a step."""
+    n = PROMPT if phase == "prefill" else BATCH
+    seqs = 1 if phase == "prefill" else BATCH
+    start = 0 if phase == "prefill" else CONTEXT - 1
+    L, H, G, d, w = z["layers"], z["heads"], z["kv_heads"], z["dim"], z["width"]
+    E, top, fe, fs, moe_layers = z["experts"], z["top"], z["expert_ff"], z["shared_ff"], z["layers"] - 1
+    steps = 1 if phase == "prefill" else 4
+    pairs = seqs * _window_pairs(n // seqs, start, z["window"], z["keep"])
+    keys_read = seqs * min(start + n // seqs, z["window"] + z["keep"] + (n // seqs if phase == "prefill" else 0))
+    attention = (L * (keys_read * G * 2 * d * 2 + n * H * d * (4 + 2)), L * 4.0 * H * d * pairs)
+    chosen = min(E, n * top)                             # experts whose weights a step of few tokens reads at most
+    work = {
+        "paged_attention_general_tc": (attention[0], attention[1], "bf16 tensor"),
+        "paged_attention_general_tiled": (attention[0], attention[1], "fp32 FMA"),
+        "paged_attention_general": (attention[0], attention[1], "fp32 FMA"),
+        "qk_prepare": (L * n * ((H + G) * d * 4 + H * d * 4 + 2 * G * d * 2), 0.0, ""),
+        "sigmoid_gate_strided": (L * n * H * d * (4 + 2 + 2), 0.0, ""),
+        "post_norm_add_bias": (2 * L * n * w * (2 + 4 + 4 + 2), 0.0, ""),
+        "glu_bias": (n * z["ff"] * (8 + 2), 0.0, ""),
+        "moe_route": (moe_layers * (n * w * 2 + E * w * 4), 0.0, ""),
+        "moe_grouped": (moe_layers * (E * 3 * w * fe * 2 + n * w * 4 + n * top * (fe * 4 + w * 8)),
+                        moe_layers * 2.0 * n * top * 3 * w * fe, "bf16 tensor"),
+        "moe_gate_up": (moe_layers * (chosen * 2 * fe * w * 2 + n * w * 2), moe_layers * 4.0 * n * top * fe * w, "fp32 FMA"),
+        "moe_down": (moe_layers * (chosen * fe * w * 2 + n * w * 4), moe_layers * 2.0 * n * top * fe * w, "fp32 FMA"),
+        "clamped_glu": (moe_layers * n * fs * 6, 0.0, ""),
+    }
+    return {k: (b * steps, f * steps, on) for k, (b, f, on) in work.items()}
+
+
 def like_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
     """The same for the dense model's kernels that do the like jobs."""
     n = PROMPT if phase == "prefill" else BATCH
-    layers, H, G, d, w = 4 * z["groups"], z["heads"], z["kv_heads"], z["dim"], z["width"]
+    layers, H, G, d, w = z["layers"] if "layers" in z else 4 * z["groups"], z["heads"], z["kv_heads"], z["dim"], z["width"]
     steps = 1 if phase == "prefill" else 4
     if phase == "prefill":
         work = {"paged_attention_prefill_tcgen05": (layers * (PROMPT * (2 * H + 2 * G) * d * 2),
@@ -203,22 +264,26 @@ def rooflines(kernels: Dict[str, List[float]], work: Dict[str, Tuple[float, floa
     return out
 
 
+DESIGNS = {"bubotar": (SIZES, bubotar_config, own_work), "topunex": (TOPUNEX_SIZES, topunex_config, topunex_work)}
+
+
 def run(args, bench) -> dict:
     """``bench``: the bench module (its timing functions, peaks and clock sampler are used as they are)."""
     import torch
     pk = bench.peaks()
-    sizes = [s for s in (args.sizes.split(",") if args.sizes else SIZES) if s]
+    table, make_config, design_work = DESIGNS[args.design]
+    sizes = [s for s in (args.sizes.split(",") if args.sizes else table) if s]
     line = {"design": args.design, "dtype": "bf16", "data": "synthetic: random weights, random token ids, random cache contents for decode",
             "prompt_tokens": PROMPT, "decode": {"batch": BATCH, "context": CONTEXT}, "peaks": pk, "sizes": {}}
     for size in sizes:
-        z = SIZES[size]
+        z = table[size]
         entry = {"shape": z}
-        for who, raw in (("design", bubotar_config(z)), ("dense", dense_config(z))):
+        for who, raw in (("design", make_config(z)), ("dense", dense_config(z))):
             engine = build(raw)
             p_seconds = bench.time_prefill(engine, PROMPT)
             d_seconds, _, _ = bench.time_decode(engine, BATCH, CONTEXT, args.steps, max(3, args.warmup))
             prefill_k, decode_k = profiled(engine, bench)
-            work = own_work if who == "design" else like_work
+            work = design_work if who == "design" else like_work
             entry[who] = {
                 "model": engine.model.spec.architecture, "weights_gb": round(engine.model.weight_bytes(0) / 1e9, 3),
                 "prefill_tokens_per_s": round(PROMPT / p_seconds, 1), "prefill_ms": round(p_seconds * 1e3, 3),

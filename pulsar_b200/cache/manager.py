@@ -56,19 +56,22 @@ class CacheNeed:
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: Optional[torch.dtype] = None   # None: the engine's activation dtype
+    keep_first: int = 0                         # with a window: the first keys of a sequence that stay visible below it
 
     @staticmethod
-    def paged(tensors: Sequence[CachedTensor], window: Optional[int] = None) -> "CacheNeed":
+    def paged(tensors: Sequence[CachedTensor], window: Optional[int] = None, keep_first: int = 0) -> "CacheNeed":
         tensors = tuple(tensors)
         names = [t.name for t in tensors]
         if not tensors or len(set(names)) != len(names) or any(t.heads <= 0 or t.width <= 0 for t in tensors):
             raise ValueError(f"a paged cache entry needs tensors with distinct names and positive sizes, found {tensors}")
-        return CacheNeed("paged_kv", tensors, window)
+        if keep_first < 0:
+            raise ValueError("the number of kept first keys must not be negative")
+        return CacheNeed("paged_kv", tensors, window, keep_first=int(keep_first) if window is not None else 0)
 
     @staticmethod
-    def paged_kv(n_kv_heads: int, head_dim: int, window: Optional[int] = None) -> "CacheNeed":
+    def paged_kv(n_kv_heads: int, head_dim: int, window: Optional[int] = None, keep_first: int = 0) -> "CacheNeed":
         """Keys and values of one shape: tensors "k" and "v"."""
-        return CacheNeed.paged((CachedTensor("k", n_kv_heads, head_dim), CachedTensor("v", n_kv_heads, head_dim)), window)
+        return CacheNeed.paged((CachedTensor("k", n_kv_heads, head_dim), CachedTensor("v", n_kv_heads, head_dim)), window, keep_first)
 
     def bytes_per_token(self, default_dtype: torch.dtype) -> int:
         return sum(t.heads * t.width * (t.dtype or default_dtype).itemsize for t in self.tensors)
@@ -162,7 +165,7 @@ class CacheManager:
         for e, need in enumerate(self.needs):
             if need.kind != "paged_kv":
                 continue
-            key = (need.tensors, need.window)
+            key = (need.tensors, need.window, need.keep_first)
             if key not in key_to_group:
                 key_to_group[key] = len(self.groups)
                 self.groups.append(_Group(need, [], None))
@@ -180,6 +183,9 @@ class CacheManager:
                                          self.max_requests)
         if not self._h:
             raise CacheError("the host runtime refused the cache's sizes")
+        for g, grp in enumerate(self.groups):
+            if grp.need.keep_first and self._lib.ph_cache_set_keep(self._h, g, int(grp.need.keep_first)) != 0:
+                raise CacheError("the host runtime refused the number of kept first keys")
         self._n_groups = len(self.groups)
         self._scratch = (ctypes.c_int * max(1, self._n_groups))()
         for g, (grp, c) in enumerate(zip(self.groups, counts)):

@@ -35,6 +35,8 @@ PH_EXPORT void* ph_cache_new(int n_groups, const int* windows, const int* pages,
     return new Cache(n_groups, windows, pages, page_size, max_requests);
 }
 PH_EXPORT void ph_cache_delete(void* h) { delete static_cast<Cache*>(h); }
+// The first keep_first keys of every sequence of this group stay visible below its window (their pages are kept).
+PH_EXPORT int ph_cache_set_keep(void* h, int group, int keep_first) { return static_cast<Cache*>(h)->set_keep(group, keep_first); }
 PH_EXPORT int ph_open(void* h, int64_t rid) { return static_cast<Cache*>(h)->open(rid); }
 PH_EXPORT int ph_has(void* h, int64_t rid) { return static_cast<Cache*>(h)->has(rid) ? 1 : 0; }
 PH_EXPORT int ph_length(void* h, int64_t rid) {

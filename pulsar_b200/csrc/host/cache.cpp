@@ -33,6 +33,12 @@ Cache::Cache(int n_groups, const int* windows, const int* pages, int page_size, 
     }
 }
 
+int Cache::set_keep(int group, int keep_first) {
+    if (group < 0 || group >= n_groups() || keep_first < 0 || !reqs_.empty()) return kBadArgument;
+    groups_[group].keep = keep_first;
+    return 0;
+}
+
 const Request* Cache::find(int64_t rid) const {
     auto it = reqs_.find(rid);
     return it == reqs_.end() ? nullptr : &it->second;
@@ -49,7 +55,8 @@ int Cache::open(int64_t rid) {
     Request r;
     r.slot = slot;
     r.tables.resize(groups_.size());
-    r.released.assign(groups_.size(), 0);
+    r.released.resize(groups_.size());
+    for (int g = 0; g < n_groups(); ++g) r.released[g] = kept_pages(g);       // the release starts behind the kept pages
     r.synced.assign(groups_.size(), 0);
     reqs_.emplace(rid, std::move(r));
     return slot;

@@ -46,13 +46,14 @@ private:
 struct Group {
     int window;                 // keys a query sees at most; <= 0: all of them
     FreeList pages;
+    int keep = 0;               // the first `keep` keys of a sequence stay visible below the window: their pages are never given back
 };
 
 struct Request {
     int length = 0;
     int slot = -1;
     std::vector<std::vector<int>> tables;     // per group: logical page -> page id, or -1 once released
-    std::vector<int> released;                // per group: logical pages [0, released) were given back
+    std::vector<int> released;                // per group: logical pages [kept pages, released) were given back
     std::vector<int> synced;                  // per group: logical pages [0, synced) are in the device's resident table
 };
 
@@ -60,6 +61,8 @@ class Cache {
 public:
     Cache(int n_groups, const int* windows, const int* pages, int page_size, int max_requests);
 
+    int set_keep(int group, int keep_first);                    // before any request is open
+    int kept_pages(int group) const { return (groups_[group].keep + page_size_ - 1) / page_size_; }
     int open(int64_t rid);                                      // state slot
     bool has(int64_t rid) const { return reqs_.count(rid) != 0; }
     const Request* find(int64_t rid) const;

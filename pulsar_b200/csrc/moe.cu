@@ -19,32 +19,76 @@ namespace {
 
 using namespace pb;
 
+constexpr int kRouteTokens = 4;          // tokens a block of the router shares an expert's row among
+
+// One block per kRouteTokens tokens; a warp takes an expert (strided), reads its row once, 16 bytes a lane with two
+// chunks in flight, and adds it up against each of the block's tokens.  A token's sums run in an order that depends on
+// the width alone, not on which tokens share its block.
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, int* __restrict__ ids,
-                                 float* __restrict__ weights, int width, int n_experts, int top, float scale, int renormalize) {
+                                 float* __restrict__ weights, int n, int width, int n_experts, int top, float scale,
+                                 int renormalize) {
     pdl_wait();
-    extern __shared__ float smem[];
-    float* x = smem;                         // [width]
-    float* s = smem + width;                 // [n_experts]
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) x[i] = to_float(h[(size_t)t * width + i]);
-    __syncthreads();
-    for (int e = warp; e < n_experts; e += warps) {
-        const float* w = router + (size_t)e * width;
-        float z = 0.0f;
-        for (int i = lane; i < width; i += 32) z = fmaf(w[i], x[i], z);
-        z = warp_sum(z);
-        if (lane == 0) s[e] = 1.0f / (1.0f + expf(-z));
+    extern __shared__ __align__(16) float smem[];
+    float* x = smem;                                     // [kRouteTokens][width]
+    float* s = smem + (size_t)kRouteTokens * width;      // [kRouteTokens][n_experts]
+    const int t0 = blockIdx.x * kRouteTokens, n_tok = min(kRouteTokens, n - t0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < kRouteTokens * width; i += blockDim.x) {
+        const int tok = i / width;
+        x[i] = tok < n_tok ? to_float(h[(size_t)t0 * width + i]) : 0.0f;
     }
     __syncthreads();
-    if (warp != 0) return;
+    const bool vec = (width & 3) == 0 && ((uintptr_t)router & 15) == 0;
+    for (int e = warp; e < n_experts; e += warps) {
+        const float* w = router + (size_t)e * width;
+        float z[kRouteTokens];
+#pragma unroll
+        for (int k = 0; k < kRouteTokens; ++k) z[k] = 0.0f;
+        if (vec) {
+            int i = lane * 4;
+            for (; i + 128 < width; i += 256) {
+                const float4 a = *reinterpret_cast<const float4*>(w + i), b = *reinterpret_cast<const float4*>(w + i + 128);
+#pragma unroll
+                for (int k = 0; k < kRouteTokens; ++k) {
+                    const float4 xa = *reinterpret_cast<const float4*>(x + k * width + i);
+                    const float4 xb = *reinterpret_cast<const float4*>(x + k * width + i + 128);
+                    z[k] = fmaf(a.x, xa.x, z[k]); z[k] = fmaf(a.y, xa.y, z[k]); z[k] = fmaf(a.z, xa.z, z[k]); z[k] = fmaf(a.w, xa.w, z[k]);
+                    z[k] = fmaf(b.x, xb.x, z[k]); z[k] = fmaf(b.y, xb.y, z[k]); z[k] = fmaf(b.z, xb.z, z[k]); z[k] = fmaf(b.w, xb.w, z[k]);
+                }
+            }
+            if (i < width) {
+                const float4 a = *reinterpret_cast<const float4*>(w + i);
+#pragma unroll
+                for (int k = 0; k < kRouteTokens; ++k) {
+                    const float4 xa = *reinterpret_cast<const float4*>(x + k * width + i);
+                    z[k] = fmaf(a.x, xa.x, z[k]); z[k] = fmaf(a.y, xa.y, z[k]); z[k] = fmaf(a.z, xa.z, z[k]); z[k] = fmaf(a.w, xa.w, z[k]);
+                }
+            }
+        } else {
+            for (int i = lane; i < width; i += 32) {
+                const float a = w[i];
+#pragma unroll
+                for (int k = 0; k < kRouteTokens; ++k) z[k] = fmaf(a, x[k * width + i], z[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kRouteTokens; ++k) {
+            const float zk = warp_sum(z[k]);
+            if (lane == 0) s[k * n_experts + e] = 1.0f / (1.0f + expf(-zk));
+        }
+    }
+    __syncthreads();
+    if (warp >= n_tok) return;                           // warp k picks for token k of the block
+    float* sk = s + (size_t)warp * n_experts;
+    const size_t t = (size_t)t0 + warp;
     float total = 0.0f;
     for (int c = 0; c < top; ++c) {
         // the largest score left; among equals the lowest index
         float best = -1.0f;
         int arg = n_experts;
         for (int e = lane; e < n_experts; e += 32)
-            if (s[e] > best) { best = s[e]; arg = e; }
+            if (sk[e] > best) { best = sk[e]; arg = e; }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
@@ -52,22 +96,62 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
         if (lane == 0) {
-            ids[(size_t)t * top + c] = arg;
-            weights[(size_t)t * top + c] = best;
-            s[arg] = -2.0f;                  // taken
+            ids[t * top + c] = arg;
+            weights[t * top + c] = best;
+            sk[arg] = -2.0f;                 // taken
         }
         total += best;
         __syncwarp();
     }
     if (lane == 0) {
         const float f = renormalize ? scale / total : scale;
-        for (int c = 0; c < top; ++c) weights[(size_t)t * top + c] *= f;
+        for (int c = 0; c < top; ++c) weights[t * top + c] *= f;
     }
 }
 
+__device__ __forceinline__ void load_chunk(const float* p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+__device__ __forceinline__ void load_chunk(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(u[i] << 16); f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+}
+template <typename T> struct Chunk;
+template <> struct Chunk<float> { static constexpr int n = 4; };
+template <> struct Chunk<__nv_bfloat16> { static constexpr int n = 8; };
+
+// The warp's sum over i of w[i] * x[i] (x in shared memory, float32).  Rows that start on a 16-byte boundary and hold
+// a whole number of 16-byte chunks are read 16 bytes a lane, two chunks in flight; the order of addition depends on
+// the row's length and alignment alone.
 template <typename T>
 __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    constexpr int V = Chunk<T>::n;
     float acc = 0.0f;
+    if (n % V == 0 && ((uintptr_t)w & 15) == 0) {
+        float acc2 = 0.0f;
+        int i = lane * V;
+        for (; i + 32 * V < n; i += 64 * V) {
+            float a[V], b[V], xa[V], xb[V];
+            load_chunk(w + i, a);
+            load_chunk(w + i + 32 * V, b);
+#pragma unroll
+            for (int e = 0; e < V; e += 4) { load_chunk(x + i + e, *reinterpret_cast<float(*)[4]>(xa + e)); load_chunk(x + i + 32 * V + e, *reinterpret_cast<float(*)[4]>(xb + e)); }
+#pragma unroll
+            for (int e = 0; e < V; ++e) { acc = fmaf(a[e], xa[e], acc); acc2 = fmaf(b[e], xb[e], acc2); }
+        }
+        if (i < n) {
+            float a[V], xa[V];
+            load_chunk(w + i, a);
+#pragma unroll
+            for (int e = 0; e < V; e += 4) load_chunk(x + i + e, *reinterpret_cast<float(*)[4]>(xa + e));
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc = fmaf(a[e], xa[e], acc);
+        }
+        return warp_sum(acc + acc2);
+    }
     for (int i = lane; i < n; i += 32) acc = fmaf(to_float(w[i]), x[i], acc);
     return warp_sum(acc);
 }
@@ -76,7 +160,7 @@ template <typename T>
 __global__ void moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gate_up, const int* __restrict__ ids,
                                    T* __restrict__ act, int width, int ff, int top, const GatedInter p) {
     pdl_wait();
-    extern __shared__ float x[];             // [width]
+    extern __shared__ __align__(16) float x[];             // [width]
     const int pair = blockIdx.x, t = pair / top;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     for (int i = threadIdx.x; i < width; i += blockDim.x) x[i] = to_float(h[(size_t)t * width + i]);
@@ -95,7 +179,7 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const T* __restrict__
                                 const float* __restrict__ weights, const T* __restrict__ add, T* __restrict__ out, int width,
                                 int ff, int top) {
     pdl_wait();
-    extern __shared__ float y[];             // [top][ff]
+    extern __shared__ __align__(16) float y[];             // [top][ff]
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     for (int i = threadIdx.x; i < top * ff; i += blockDim.x) y[i] = to_float(act[(size_t)t * top * ff + i]);
@@ -117,14 +201,27 @@ PB_EXPORT int pb_moe_route(int dtype, const void* h, const float* router, int* i
                            int top, float scale, int renormalize, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (width <= 0 || n_experts <= 0 || top <= 0 || top > n_experts) return PB_ERR_BAD_SIZE;
-    const size_t smem = sizeof(float) * ((size_t)width + n_experts);
-    if (smem > 48 * 1024) return PB_ERR_TOO_LARGE;
-    if (dtype == PB_F32)
-        return launch_pdl(moe_route_kernel<float>, dim3(n), dim3(128), smem, stream, (const float*)h, router, ids, weights, width,
-                          n_experts, top, scale, renormalize);
-    if (dtype == PB_BF16)
-        return launch_pdl(moe_route_kernel<__nv_bfloat16>, dim3(n), dim3(128), smem, stream, (const __nv_bfloat16*)h, router, ids,
-                          weights, width, n_experts, top, scale, renormalize);
+    const size_t smem = sizeof(float) * kRouteTokens * ((size_t)width + n_experts);
+    if (smem > 200 * 1024) return PB_ERR_TOO_LARGE;
+    int threads = 32 * n_experts;                        // a warp per expert where that fits a block
+    if (threads > 1024) threads = 1024;
+    if (threads < 32 * kRouteTokens) threads = 32 * kRouteTokens;
+    const int blocks = (n + kRouteTokens - 1) / kRouteTokens;
+    cudaError_t ce = cudaSuccess;
+    if (dtype == PB_F32) {
+        static size_t allowed = 48 * 1024;
+        if (smem > allowed) { ce = cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
+        if (ce != cudaSuccess) return (int)ce;
+        return launch_pdl(moe_route_kernel<float>, dim3(blocks), dim3(threads), smem, stream, (const float*)h, router, ids, weights, n,
+                          width, n_experts, top, scale, renormalize);
+    }
+    if (dtype == PB_BF16) {
+        static size_t allowed = 48 * 1024;
+        if (smem > allowed) { ce = cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
+        if (ce != cudaSuccess) return (int)ce;
+        return launch_pdl(moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), smem, stream, (const __nv_bfloat16*)h, router, ids,
+                          weights, n, width, n_experts, top, scale, renormalize);
+    }
     return PB_ERR_BAD_DTYPE;
 }
 

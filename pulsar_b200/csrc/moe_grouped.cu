@@ -6,8 +6,8 @@
 //                   tile_row0[t] .. of expert tile_expert[t]; meta[0] = number of tiles.  One block; nothing returns to the host.
 //   moe_grouped     mode 0: act[sorted row] = gated(h[token] Wg[e]^T, h[token] Wu[e]^T)   (rows gathered by pair / top)
 //                   mode 1: y[pair] (float32) = act[sorted row] W_down[e]^T                (rows scattered back to their pair)
-//                   mma.sync m16n8k16, bfloat16 operands, float32 accumulators; tiles of 64 rows x 64 output columns
-//                   (mode 0: 64 gate and the 64 up columns that go with them), K in steps of 32 through a two-stage cp.async
+//                   mma.sync m16n8k16, bfloat16 operands, float32 accumulators; tiles of 128 rows x 64 output columns
+//                   (mode 0: 64 gate and the 64 up columns that go with them), K in steps of 32 through a three-stage cp.async
 //                   pipeline.  The grid has as many row tiles as the worst case needs; blocks beyond meta[0] return at once.
 //   moe_combine     out[n] = add[n] + sum over the slots, in their order, of weight[n, slot] * y[n * top + slot]; float32 sums,
 //                   one rounding.
@@ -19,7 +19,7 @@ namespace {
 
 using namespace pb;
 
-constexpr int kBM = 64, kBN = 64, kBK = 32, kPad = 8;
+constexpr int kBM = 128, kBN = 64, kBK = 32, kPad = 8, kStages = 3, kThreads = 256;
 constexpr int kRow = kBK + kPad;                       // shared-memory row stride in elements (80 bytes)
 
 __global__ void moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int* __restrict__ offsets,
@@ -52,17 +52,20 @@ __global__ void moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int n_
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) sorted[atomicAdd(&cursor[ids[p]], 1)] = p;
 }
 
-// MODE 0: gate/up with the gating; MODE 1: down.
+// MODE 0: gate/up with the gating; MODE 1: down.  Eight warps, four along the rows and two along the columns: a warp owns
+// 32 rows x 32 output columns (mode 0: 32 gate columns and the 32 up columns that go with them).
 template <int MODE>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kThreads)
 moe_grouped_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const int* __restrict__ offsets,
                    const int* __restrict__ sorted, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                    const int* __restrict__ meta, bf16* __restrict__ act_out, float* __restrict__ y_out, int K, int n_out, int top,
                    const GatedInter gating) {
     pdl_wait();
     constexpr int kWRows = MODE == 0 ? 2 * kBN : kBN;
-    __shared__ __align__(16) bf16 a_s[2][kBM * kRow];
-    __shared__ __align__(16) bf16 w_s[2][kWRows * kRow];
+    constexpr int kParts = MODE == 0 ? 2 : 1;              // gate and up, or one
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* a_s = reinterpret_cast<bf16*>(smem_raw);                               // [stages][kBM][kRow]
+    bf16* w_s = a_s + kStages * kBM * kRow;                                       // [stages][kWRows][kRow]
     __shared__ int src_row[kBM];
     const int tile = blockIdx.x;
     if (tile >= meta[0]) return;
@@ -70,6 +73,7 @@ moe_grouped_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
     const int rows = min(kBM, offsets[e + 1] - row0);
     const int n0 = blockIdx.y * kBN;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_m = warp >> 1, warp_n = warp & 1;
     if (tid < kBM) {
         int r = -1;
         if (tid < rows) r = MODE == 0 ? sorted[row0 + tid] / top : row0 + tid;
@@ -79,83 +83,101 @@ moe_grouped_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
     const bf16* w_e = w + (size_t)e * (MODE == 0 ? 2 : 1) * n_out * K;
 
     auto issue = [&](int k0, int stage) {
-        // A: 64 rows x 4 chunks of 8 elements
-        for (int c = tid; c < kBM * (kBK / 8); c += 128) {
+        bf16* as = a_s + stage * kBM * kRow;
+        bf16* ws = w_s + stage * kWRows * kRow;
+        for (int c = tid; c < kBM * (kBK / 8); c += kThreads) {
             const int r = c / (kBK / 8), part = c % (kBK / 8);
             const int k = k0 + part * 8;
             const bool ok = src_row[r] >= 0 && k < K;
-            cp_async16(smem_u32(&a_s[stage][r * kRow + part * 8]), ok ? a + (size_t)src_row[r] * K + k : a, ok);
+            cp_async16(smem_u32(as + r * kRow + part * 8), ok ? a + (size_t)src_row[r] * K + k : a, ok);
         }
-        for (int c = tid; c < kWRows * (kBK / 8); c += 128) {
+        for (int c = tid; c < kWRows * (kBK / 8); c += kThreads) {
             const int r = c / (kBK / 8), part = c % (kBK / 8);
             const int k = k0 + part * 8;
             const int col = n0 + (r % kBN);
             const bool ok = col < n_out && k < K;
             const size_t wr = MODE == 0 ? (size_t)(r / kBN) * n_out + col : (size_t)col;      // up rows follow the gate rows
-            cp_async16(smem_u32(&w_s[stage][r * kRow + part * 8]), ok ? w_e + wr * K + k : w_e, ok);
+            cp_async16(smem_u32(ws + r * kRow + part * 8), ok ? w_e + wr * K + k : w_e, ok);
         }
     };
 
-    float acc[kWRows / 8][4];
+    float acc[2][4 * kParts][4];
 #pragma unroll
-    for (int i = 0; i < kWRows / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f; }
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int i = 0; i < 4 * kParts; ++i) { acc[mi][i][0] = acc[mi][i][1] = acc[mi][i][2] = acc[mi][i][3] = 0.0f; }
 
     const int k_steps = (K + kBK - 1) / kBK;
-    issue(0, 0);
-    cp_async_commit();
-    for (int ks = 0; ks < k_steps; ++ks) {
-        if (ks + 1 < k_steps) issue((ks + 1) * kBK, (ks + 1) & 1);
+#pragma unroll
+    for (int st = 0; st < kStages - 1; ++st) {
+        if (st < k_steps) issue(st * kBK, st);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        const int stage = ks & 1;
-        if (warp * 16 < rows) {
+    }
+    for (int ks = 0; ks < k_steps; ++ks) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();                                   // stage ks has landed; everyone is done with stage ks - 1
+        if (ks + kStages - 1 < k_steps) issue((ks + kStages - 1) * kBK, (ks + kStages - 1) % kStages);
+        cp_async_commit();
+        const bf16* as = a_s + (ks % kStages) * kBM * kRow;
+        const bf16* ws = w_s + (ks % kStages) * kWRows * kRow;
+        if (warp_m * 32 < rows) {
 #pragma unroll
             for (int kk = 0; kk < kBK / 16; ++kk) {
-                uint32_t af[4];
-                ldmatrix_x4(af, smem_u32(&a_s[stage][(warp * 16 + (lane & 15)) * kRow + kk * 16 + (lane >> 4) * 8]));
+                uint32_t af[2][4];
 #pragma unroll
-                for (int nn = 0; nn < kWRows / 16; ++nn) {
-                    uint32_t bfr[4];
-                    const int r = nn * 16 + (lane & 7) + ((lane >> 4) << 3);
-                    ldmatrix_x4(bfr, smem_u32(&w_s[stage][r * kRow + kk * 16 + ((lane >> 3) & 1) * 8]));
-                    mma_bf16(acc[2 * nn], af, bfr[0], bfr[1]);
-                    mma_bf16(acc[2 * nn + 1], af, bfr[2], bfr[3]);
-                }
+                for (int mi = 0; mi < 2; ++mi)
+                    ldmatrix_x4(af[mi], smem_u32(as + (warp_m * 32 + mi * 16 + (lane & 15)) * kRow + kk * 16 + (lane >> 4) * 8));
+#pragma unroll
+                for (int part = 0; part < kParts; ++part)
+#pragma unroll
+                    for (int nn = 0; nn < 2; ++nn) {
+                        uint32_t bfr[4];
+                        const int r = part * kBN + warp_n * 32 + nn * 16 + (lane & 7) + ((lane >> 4) << 3);
+                        ldmatrix_x4(bfr, smem_u32(ws + r * kRow + kk * 16 + ((lane >> 3) & 1) * 8));
+#pragma unroll
+                        for (int mi = 0; mi < 2; ++mi) {
+                            mma_bf16(acc[mi][part * 4 + 2 * nn], af[mi], bfr[0], bfr[1]);
+                            mma_bf16(acc[mi][part * 4 + 2 * nn + 1], af[mi], bfr[2], bfr[3]);
+                        }
+                    }
             }
         }
-        __syncthreads();
     }
     cp_async_wait<0>();
 
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int r = warp * 16 + g + half * 8;
-        if (r >= rows) continue;
-        if (MODE == 0) {
-            bf16* dst = act_out + (size_t)(row0 + r) * n_out;
+    for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
-            for (int j = 0; j < kBN / 8; ++j) {
-                const int col = n0 + j * 8 + 2 * t;
-                const float v0 = gated(acc[j][2 * half], acc[j + kBN / 8][2 * half], gating);
-                const float v1 = gated(acc[j][2 * half + 1], acc[j + kBN / 8][2 * half + 1], gating);
-                if (col + 1 < n_out && (n_out & 1) == 0) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(v0, v1);
-                else {
-                    if (col < n_out) dst[col] = __float2bfloat16_rn(v0);
-                    if (col + 1 < n_out) dst[col + 1] = __float2bfloat16_rn(v1);
+        for (int half = 0; half < 2; ++half) {
+            const int r = warp_m * 32 + mi * 16 + g + half * 8;
+            if (r >= rows) continue;
+            if (MODE == 0) {
+                bf16* dst = act_out + (size_t)(row0 + r) * n_out;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int col = n0 + warp_n * 32 + j * 8 + 2 * t;
+                    const float v0 = gated(acc[mi][j][2 * half], acc[mi][j + 4 * (kParts - 1)][2 * half], gating);
+                    const float v1 = gated(acc[mi][j][2 * half + 1], acc[mi][j + 4 * (kParts - 1)][2 * half + 1], gating);
+                    if (col + 1 < n_out && (n_out & 1) == 0) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(v0, v1);
+                    else {
+                        if (col < n_out) dst[col] = __float2bfloat16_rn(v0);
+                        if (col + 1 < n_out) dst[col + 1] = __float2bfloat16_rn(v1);
+                    }
+                }
+            } else {
+                float* dst = y_out + (size_t)sorted[row0 + r] * n_out;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int col = n0 + warp_n * 32 + j * 8 + 2 * t;
+                    if (col + 1 < n_out && (n_out & 1) == 0) *reinterpret_cast<float2*>(dst + col) = make_float2(acc[mi][j][2 * half], acc[mi][j][2 * half + 1]);
+                    else {
+                        if (col < n_out) dst[col] = acc[mi][j][2 * half];
+                        if (col + 1 < n_out) dst[col + 1] = acc[mi][j][2 * half + 1];
+                    }
                 }
             }
-        } else {
-            float* dst = y_out + (size_t)sorted[row0 + r] * n_out;
-#pragma unroll
-            for (int j = 0; j < kBN / 8; ++j) {
-                const int col = n0 + j * 8 + 2 * t;
-                if (col < n_out) dst[col] = acc[j][2 * half];
-                if (col + 1 < n_out) dst[col + 1] = acc[j][2 * half + 1];
-            }
         }
-    }
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const bf16* __restrict__ add,
@@ -201,11 +223,19 @@ PB_EXPORT int pb_moe_grouped(const void* h, const void* w_gate_up, const void* w
                         tile_expert, tile_row0, meta);
     if (rc != 0) return rc;
     const GatedInter gating(ff, limit > 0.0f ? limit : __builtin_huge_valf(), alpha, shift);
-    rc = launch_pdl(moe_grouped_kernel<0>, dim3(tiles, (ff + kBN - 1) / kBN), dim3(128), 0, stream, (const bf16*)h, (const bf16*)w_gate_up,
+    constexpr int smem0 = kStages * (kBM + 2 * kBN) * kRow * 2, smem1 = kStages * (kBM + kBN) * kRow * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t ce = cudaFuncSetAttribute(moe_grouped_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem0);
+        if (ce == cudaSuccess) ce = cudaFuncSetAttribute(moe_grouped_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1);
+        if (ce != cudaSuccess) return (int)ce;
+        configured = true;
+    }
+    rc = launch_pdl(moe_grouped_kernel<0>, dim3(tiles, (ff + kBN - 1) / kBN), dim3(kThreads), smem0, stream, (const bf16*)h, (const bf16*)w_gate_up,
                     (const int*)offsets, (const int*)sorted, (const int*)tile_expert, (const int*)tile_row0, (const int*)meta, (bf16*)act,
                     (float*)nullptr, width, ff, top, gating);
     if (rc != 0) return rc;
-    rc = launch_pdl(moe_grouped_kernel<1>, dim3(tiles, (width + kBN - 1) / kBN), dim3(128), 0, stream, (const bf16*)act,
+    rc = launch_pdl(moe_grouped_kernel<1>, dim3(tiles, (width + kBN - 1) / kBN), dim3(kThreads), smem1, stream, (const bf16*)act,
                     (const bf16*)w_down, (const int*)offsets, (const int*)sorted, (const int*)tile_expert, (const int*)tile_row0,
                     (const int*)meta, (bf16*)nullptr, y, ff, width, top, gating);
     if (rc != 0) return rc;

@@ -18,6 +18,7 @@ _SIGNATURES = {
     "ph_freelist_give": (_I, [_P, _I]), "ph_freelist_n": (_I, [_P]), "ph_freelist_n_free": (_I, [_P]),
     "ph_freelist_held": (_I, [_P, _I]),
     "ph_cache_new": (_P, [_I, _IP, _IP, _I, _I]), "ph_cache_delete": (None, [_P]),
+    "ph_cache_set_keep": (_I, [_P, _I, _I]),
     "ph_open": (_I, [_P, _L]), "ph_has": (_I, [_P, _L]), "ph_length": (_I, [_P, _L]), "ph_state_slot": (_I, [_P, _L]),
     "ph_n_logical_pages": (_I, [_P, _L]), "ph_pages_to_append": (_I, [_P, _L, _I, _IP]), "ph_reclaimable": (_I, [_P, _L, _IP]),
     "ph_can_append": (_I, [_P, _L, _I]), "ph_can_admit": (_I, [_P, _I]), "ph_release_passed": (_I, [_P, _L]),

@@ -936,13 +936,17 @@ GENERAL_TC = os.environ.get("PULSAR_GENERAL_TC", "1") != "0"
 GENERAL_TC_MIN = 16
 
 
+_GENERAL_SLOTS = 592         # four blocks of the tiled general attention on each of the 148 SMs: a block's tiles load and compute in
+                             # turn, so short runs of tiles in many blocks hide what one block cannot
+
+
 def general_splits(blocks: int, table_tokens: int) -> int:
-    """Splits of the keys for the tiled general attention: as many as bring the grid to two blocks per SM, at most 32 and
+    """Splits of the keys for the tiled general attention: as many as bring the grid to four blocks per SM, at most 32 and
     at most one per 64 tokens that the block table can name.  A function of the step's shape alone (not of the lengths),
     so that a captured step stays valid while its sequences grow."""
-    if blocks >= _DECODE_SLOTS:
+    if blocks >= _GENERAL_SLOTS:
         return 1
-    return max(1, min(32, _DECODE_SLOTS // max(1, blocks), table_tokens // 64))
+    return max(1, min(32, _GENERAL_SLOTS // max(1, blocks), table_tokens // 64))
 
 
 def paged_attention_general(ctx, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,

@@ -139,13 +139,11 @@ class Attention(Mixer):
 
     def cache_need(self) -> CacheNeed:
         s = self.spec
-        # Pages behind a window go back to the pool as the queries pass them; with kept first keys every page stays
-        # (the kept keys' pages are needed for good, and the manager releases from the front only).
-        window = None if s.keep_first else s.window
+        # Pages behind a window go back to the pool as the queries pass them, except those of the kept first keys.
         if s.value_dim != s.head_dim:
             return CacheNeed.paged((CachedTensor("k", s.n_kv_heads, s.head_dim), CachedTensor("v", s.n_kv_heads, s.value_dim)),
-                                   window)
-        return CacheNeed.paged_kv(s.n_kv_heads, s.head_dim, window)
+                                   s.window, s.keep_first)
+        return CacheNeed.paged_kv(s.n_kv_heads, s.head_dim, s.window, s.keep_first)
 
     # ---------------------------------------------------------------- one step
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: CacheView) -> torch.Tensor:

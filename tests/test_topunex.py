@@ -105,8 +105,9 @@ def test_config_becomes_parts():
     assert not {"l0.mix.v", "l2.norm2", "l2.mlp.gate", "l3.mlp.shared.gate", "l1.mlp.e5.gate", "l1.mlp.e0.gate.b"} & names
     needs = model.cache_needs()
     assert [n.kind for n in needs] == ["paged_kv"] * 4 and needs[1].tensors[0].heads == 3 and needs[1].tensors[1].width == 8
-    # kept first keys keep every page; a window alone lets the manager give pages back
-    assert needs[0].window is None and needs[2].window == 9 and needs[3].window is None
+    # pages behind a window go back to the pool, those of the kept first keys stay
+    assert (needs[0].window, needs[0].keep_first) == (11, 3) and (needs[2].window, needs[2].keep_first) == (9, 0)
+    assert needs[3].window is None and needs[3].keep_first == 0
 
 
 @pytest.mark.parametrize("edit,match", [
@@ -357,21 +358,12 @@ def _step_context(q_lens, kv_lens):
 
 
 def _dense_attention(q, k, v, scale, window, keep_first, softcap, sink, first=0):
-    """q [Lq, H, D] at positions first .. first + Lq - 1 over keys/values [L, H, D]: one row at a time."""
-    Lq, H, _ = q.shape
-    out = torch.zeros(Lq, H, v.shape[2], dtype=torch.float64)
-    for r in range(Lq):
-        i = first + r
-        js = [j for j in range(i + 1) if (window is None or i - j < window or j < keep_first)]
-        for h in range(H):
-            s = torch.stack([q[r, h] @ k[j, h] for j in js]) * scale
-            if softcap:
-                s = softcap * torch.tanh(s / softcap)
-            m = max(float(s.max()), float(sink[h]) if sink is not None else -1e30)
-            e = torch.exp(s - m)
-            den = e.sum() + (math.exp(float(sink[h]) - m) if sink is not None else 0.0)
-            out[r, h] = (e[:, None] * v[js, h]).sum(0) / den
-    return out
+    """q [Lq, H, D] at positions first .. first + Lq - 1 over keys/values [L, H, D], with the oracle's mask, cap and sink."""
+    L = k.shape[0]
+    vis = plain.visible_keys(L, window, keep_first)[first:first + q.shape[0]]
+    scores = plain.capped(torch.einsum("ihd,jhd->hij", q, k) * scale, softcap)
+    p = plain.softmax_with_sink(scores, vis[None], sink)
+    return torch.einsum("hij,jhd->ihd", p, v)
 
 
 @gpu
