@@ -7,7 +7,7 @@
 //   moe_grouped     mode 0: act[sorted row] = gated(h[token] Wg[e]^T, h[token] Wu[e]^T)   (rows gathered by pair / top)
 //                   mode 1: y[pair] (float32) = act[sorted row] W_down[e]^T                (rows scattered back to their pair)
 //                   mma.sync m16n8k16, bfloat16 operands, float32 accumulators; tiles of 128 rows x 64 output columns
-//                   (mode 0: 64 gate and the 64 up columns that go with them), K in steps of 32 through a three-stage cp.async
+//                   (mode 0: 64 gate and the 64 up columns that go with them), K in steps of 64 through a three-stage cp.async
 //                   pipeline.  The grid has as many row tiles as the worst case needs; blocks beyond meta[0] return at once.
 //   moe_combine     out[n] = add[n] + sum over the slots, in their order, of weight[n, slot] * y[n * top + slot]; float32 sums,
 //                   one rounding.
@@ -19,8 +19,8 @@ namespace {
 
 using namespace pb;
 
-constexpr int kBM = 128, kBN = 64, kBK = 32, kPad = 8, kStages = 3, kThreads = 256;
-constexpr int kRow = kBK + kPad;                       // shared-memory row stride in elements (80 bytes)
+constexpr int kBM = 128, kBN = 64, kBK = 64, kPad = 8, kStages = 3, kThreads = 256;
+constexpr int kRow = kBK + kPad;                       // shared-memory row stride in elements (144 bytes: eight rows fall on eight different 16-byte columns of the banks)
 
 __global__ void moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int* __restrict__ offsets,
                                 int* __restrict__ sorted, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
