@@ -110,6 +110,24 @@ def test_window_gives_pages_back_once_every_query_has_passed_them():
     assert m.n_free_pages() == [6]
 
 
+def test_kept_first_keys_keep_their_pages_behind_the_window():
+    """A window of 6 with 5 kept first keys on pages of 4: logical pages 0 and 1 hold kept keys and are never given
+    back; the pages between them and the window are, as soon as every future query has passed them."""
+    m = CacheManager([CacheNeed.paged_kv(2, 16, 6, keep_first=5), CacheNeed.paged_kv(2, 16, 6)], 4, 12, 2)
+    assert len(m.groups) == 2 and m.groups[0].need.keep_first == 5 and m.groups[1].need.keep_first == 0
+    m.open("a")
+    m.append("a", 9)
+    for _ in range(31):
+        m.append("a", 1)                     # length 40: the query at 40 sees keys 35 .. 40 and, in the first group, 0 .. 4
+    kept, plain = m.table("a", 0), m.table("a", 1)
+    assert kept[0] >= 0 and kept[1] >= 0 and all(p == -1 for p in kept[2:8]) and kept[8] >= 0
+    assert all(p == -1 for p in plain[:8]) and plain[8] >= 0
+    m.check_consistency()
+    m.close("a")
+    assert m.n_free_pages() == [12, 12]
+    assert CacheNeed.paged_kv(2, 16, None, keep_first=5).keep_first == 0        # without a window nothing is given back anyway
+
+
 def test_groups_with_and_without_window_share_one_request():
     m = manager(pages=10, page=4, window=5, two_groups=True)
     m.open("a")
