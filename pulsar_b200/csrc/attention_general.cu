@@ -340,6 +340,7 @@ general_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pool, 
         }
         __syncthreads();
 
+        if (warp * 4 >= n_rows) continue;                  // a warp without rows only helps to load (a step of single tokens: the group's heads are all the rows there are)
         // scores of key `lane` against the warp's four rows
         float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         const T* kr = k_s + (size_t)lane * ts.k_row;

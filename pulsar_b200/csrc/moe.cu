@@ -124,33 +124,40 @@ template <> struct Chunk<float> { static constexpr int n = 4; };
 template <> struct Chunk<__nv_bfloat16> { static constexpr int n = 8; };
 
 // The warp's sum over i of w[i] * x[i] (x in shared memory, float32).  Rows that start on a 16-byte boundary and hold
-// a whole number of 16-byte chunks are read 16 bytes a lane, two chunks in flight; the order of addition depends on
+// a whole number of 16-byte chunks are read 16 bytes a lane, four chunks in flight; the order of addition depends on
 // the row's length and alignment alone.
 template <typename T>
 __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x, int n, int lane) {
     constexpr int V = Chunk<T>::n;
+    constexpr int U = 4;                                 // chunks a lane has in flight
     float acc = 0.0f;
     if (n % V == 0 && ((uintptr_t)w & 15) == 0) {
-        float acc2 = 0.0f;
+        float part[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) part[u] = 0.0f;
         int i = lane * V;
-        for (; i + 32 * V < n; i += 64 * V) {
-            float a[V], b[V], xa[V], xb[V];
-            load_chunk(w + i, a);
-            load_chunk(w + i + 32 * V, b);
+        for (; i + (U - 1) * 32 * V < n; i += U * 32 * V) {
+            float a[U][V];
 #pragma unroll
-            for (int e = 0; e < V; e += 4) { load_chunk(x + i + e, *reinterpret_cast<float(*)[4]>(xa + e)); load_chunk(x + i + 32 * V + e, *reinterpret_cast<float(*)[4]>(xb + e)); }
+            for (int u = 0; u < U; ++u) load_chunk(w + i + u * 32 * V, a[u]);
 #pragma unroll
-            for (int e = 0; e < V; ++e) { acc = fmaf(a[e], xa[e], acc); acc2 = fmaf(b[e], xb[e], acc2); }
+            for (int u = 0; u < U; ++u) {
+                float xa[V];
+#pragma unroll
+                for (int e = 0; e < V; e += 4) load_chunk(x + i + u * 32 * V + e, *reinterpret_cast<float(*)[4]>(xa + e));
+#pragma unroll
+                for (int e = 0; e < V; ++e) part[u] = fmaf(a[u][e], xa[e], part[u]);
+            }
         }
-        if (i < n) {
+        for (; i < n; i += 32 * V) {
             float a[V], xa[V];
             load_chunk(w + i, a);
 #pragma unroll
             for (int e = 0; e < V; e += 4) load_chunk(x + i + e, *reinterpret_cast<float(*)[4]>(xa + e));
 #pragma unroll
-            for (int e = 0; e < V; ++e) acc = fmaf(a[e], xa[e], acc);
+            for (int e = 0; e < V; ++e) part[0] = fmaf(a[e], xa[e], part[0]);
         }
-        return warp_sum(acc + acc2);
+        return warp_sum((part[0] + part[1]) + (part[2] + part[3]));
     }
     for (int i = lane; i < n; i += 32) acc = fmaf(to_float(w[i]), x[i], acc);
     return warp_sum(acc);

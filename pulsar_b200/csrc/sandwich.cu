@@ -151,6 +151,48 @@ __global__ void post_norm_add_bias_kernel(float* __restrict__ residual, const T*
     for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)r * width + i] = from_float<T>(res[i]);
 }
 
+// The same with the row in registers and 16-byte accesses (width % 4 == 0, 16-byte aligned rows, delta given).
+template <typename T, int VPT>
+__global__ void post_norm_add_bias_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ bias,
+                                              const float* __restrict__ w_post, float eps_post, T* __restrict__ out, int width) {
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float* res = residual + (size_t)r * width;
+    const T* del = delta + (size_t)r * width;
+    float x[VPT][4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+        if (i < width) {
+            load4(del + i, x[v]);
+            if (bias != nullptr) {
+                float b[4];
+                load4(bias + i, b);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) x[v][e] += b[e];
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss += x[v][e] * x[v][e];
+        }
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps_post);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+        if (i < width) {
+            float rv[4], wv[4];
+            load4(res + i, rv);
+            load4(w_post + i, wv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[v][e] = rv[e] + x[v][e] * inv * wv[e];
+            store4(res + i, x[v]);
+            if (out != nullptr) store4(out + (size_t)r * width + i, x[v]);
+        }
+    }
+}
+
 template <typename TIn, typename T>
 __global__ void glu_bias_kernel(const TIn* __restrict__ gate_up, const float* __restrict__ bias, T* __restrict__ out, size_t total,
                                 const GatedInter p) {
@@ -221,6 +263,17 @@ PB_EXPORT int pb_post_norm_add_bias(int dtype, float* residual, const void* delt
                                     float eps_post, void* out, int n, int width, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (width <= 0 || (delta == nullptr && out == nullptr) || (delta != nullptr && w_post == nullptr)) return PB_ERR_BAD_SIZE;
+    const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)bias | (uintptr_t)w_post | (uintptr_t)out) & 15) == 0;
+    if (delta != nullptr && width % 4 == 0 && width <= 8192 && aligned && (dtype == PB_F32 || dtype == PB_BF16)) {
+        const int vecs = width / 4;
+        const int vpt = vecs <= 1024 ? 1 : 2;
+        const int threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;
+#define PB_POSTB(T, V) return launch_pdl(post_norm_add_bias_vec_kernel<T, V>, dim3(n), dim3(threads), 0, stream, residual, (const T*)delta, bias, \
+                                         w_post, eps_post, (T*)out, width)
+        if (dtype == PB_F32) { if (vpt == 1) PB_POSTB(float, 1); else PB_POSTB(float, 2); }
+        else { if (vpt == 1) PB_POSTB(__nv_bfloat16, 1); else PB_POSTB(__nv_bfloat16, 2); }
+#undef PB_POSTB
+    }
     const int b = block_for(width);
     if (dtype == PB_F32)
         return launch_pdl(post_norm_add_bias_kernel<float>, dim3(n), dim3(b), 0, stream, residual, (const float*)delta, bias, w_post,

@@ -449,17 +449,19 @@ def test_small_kernels_against_their_formulas(dtype):
         s = int(slots[t])
         close(k_pool[s // page, :, s % page], want_k[t], "key page")
         close(v_pool[s // page, :, s % page], k[t], "value page")
-    # the kernel behind a sublayer
-    width = 44
-    res, delta, bias, w = rnd(n, width), rnd(n, width).to(dtype), rnd(width), 1 + 0.1 * rnd(width)
-    stream = res.clone().cuda()
-    out = torch.empty(n, width, dtype=dtype, device="cuda")
-    ops.post_norm_add_bias(stream, delta.cuda(), bias.cuda(), w.cuda(), 1e-5, out)
-    want = res.double() + plain.rms_norm(delta.double() + bias.double(), w.double(), 1e-5)
-    close(stream, want, "stream", 1e-6)
-    close(out, want, "rounded stream")
-    ops.post_norm_add_bias(stream, None, None, None, 0.0, out)
-    close(out, want, "copy of the stream")
+    # the kernel behind a sublayer: rows of 16-byte pieces (held in registers), odd rows, and rows of two pieces a thread
+    for width in (44, 45, 4200):
+        res, delta, bias, w = rnd(n, width), rnd(n, width).to(dtype), rnd(width), 1 + 0.1 * rnd(width)
+        stream = res.clone().cuda()
+        out = torch.empty(n, width, dtype=dtype, device="cuda")
+        ops.post_norm_add_bias(stream, delta.cuda(), bias.cuda(), w.cuda(), 1e-5, out)
+        want = res.double() + plain.rms_norm(delta.double() + bias.double(), w.double(), 1e-5)
+        close(stream, want, f"stream of width {width}", 1e-6)
+        close(out, want, "rounded stream")
+        ops.post_norm_add_bias(stream, None, None, None, 0.0, out)
+        close(out, want, "copy of the stream")
+        ops.post_norm_add_bias(stream, delta.cuda(), None, w.cuda(), 1e-5, None)
+        close(stream, want + plain.rms_norm(delta.double(), w.double(), 1e-5), "without bias and copy", 1e-6)
     # gated units with biases; gate on the heads; bias alone
     inter = 18
     gu, b = rnd(n, 2 * inter), rnd(2 * inter)
