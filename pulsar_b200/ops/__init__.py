@@ -1309,7 +1309,7 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights
 # expert's rows through tensor-core tiles; fewer tokens read each chosen expert's weights per token.  PULSAR_MOE_GROUPED=0
 # leaves the grouped products out.
 MOE_GROUPED = os.environ.get("PULSAR_MOE_GROUPED", "1") != "0"
-MOE_GROUPED_MIN = 16
+MOE_GROUPED_MIN = int(os.environ.get("PULSAR_MOE_GROUPED_MIN", "16") or 16)
 
 
 def moe_grouped_supported(dtype: torch.dtype, width: int, ff: int, n_experts: int) -> bool:
