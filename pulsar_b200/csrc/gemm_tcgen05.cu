@@ -422,6 +422,153 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
 }
 
+// The grouped form: the rows of x are sorted by group (a mixture's (token, expert) pairs by expert), every group has a weight
+// matrix of its own (`w_rows` rows of the stacked W each), and the row tiles are listed on the device: tile t covers rows
+// tile_row0[t] .. of group tile_group[t], whose rows end before offsets[group + 1]; meta[0] tiles are listed.  A tile
+// loads 128 rows from its first row on (what lies behind the group's last row belongs to the next group and is computed
+// but not stored).  Everything else, roles, barriers and bounded waits included, is the kernel above.
+template <int MODE, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                            OutT* __restrict__ out, int N, int K, const GatedInter inter, int n_tiles, int w_rows,
+                            const int* __restrict__ offsets, const int* __restrict__ tile_group,
+                            const int* __restrict__ tile_row0, const int* __restrict__ meta) {
+    const int m_tiles = meta[0];
+    extern __shared__ unsigned char smem_raw[];
+    // 128-byte swizzled tiles want 1024-byte alignment.
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);   // full[4], empty[4], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccumulators);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int kTileCols = (MODE == kSwiGLU) ? kBN / 2 : kBN;        // output columns of a tile
+    const int k_tiles = (K + kBK - 1) / kBK;
+    const int total_tiles = m_tiles * n_tiles;
+    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + kStages);
+    const uint32_t acc_full0 = smem_addr(bars + 2 * kStages), acc_empty0 = smem_addr(bars + 2 * kStages + kAccumulators);
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < kAccumulators; ++a) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {            // one warp allocates the accumulator columns and keeps the right to free them
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemColumns));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;                                  // k-slices issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int rt = tile % m_tiles, n0 = (tile / m_tiles) * kTileCols;
+                const int m0 = tile_row0[rt], w0 = tile_group[rt] * w_rows;
+                bool ok = true;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(empty0 + 8 * s, ((it / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t a_dst = smem_addr(smem + s * kStageBytes), b_dst = a_dst + kABytes;
+                    mbar_expect_tx(full0 + 8 * s, kStageBytes);
+                    tma_load_2d(a_dst, &map_x, full0 + 8 * s, kt * kBK, m0);
+                    tma_load_2d(b_dst, &map_w, full0 + 8 * s, kt * kBK, w0 + n0);
+                    tma_load_2d(b_dst + kBBytes / 2, &map_w, full0 + 8 * s, kt * kBK, w0 + (MODE == kSwiGLU ? (int)inter : kBN / 2) + n0);
+                }
+                if (!ok) { *abort_flag = 1; atomicMax(&g_tc5_error, 2u); break; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the warp walks the loop uniformly, one elected lane issues
+        {
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+            const uint64_t desc0 = umma_desc(smem_addr(smem));
+            uint32_t it = 0;
+            int j = 0;                                        // tiles done by this block
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+                const int acc = j & 1;
+                ok = mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained it
+                const uint32_t tmem_d = tmem_u + acc * kBN;
+                for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(full0 + 8 * s, (it / kStages) & 1, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t a_desc = desc0 + (uint64_t)((uint32_t)s * (kStageBytes >> 4));
+                    const uint64_t b_desc = a_desc + (uint64_t)(kABytes >> 4);
+                    if (elect_one()) {
+#pragma unroll
+                        for (int k = 0; k < kBK / 16; ++k)      // 16 bfloat16 = 32 bytes further along the 128-byte row
+                            umma_bf16(tmem_d, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), (kt > 0 || k > 0) ? 1u : 0u);
+                        umma_commit(empty0 + 8 * s);          // the stage is free once the tensor core has read it
+                        if (kt == k_tiles - 1) umma_commit(acc_full0 + 8 * acc);     // the accumulator is complete once its MMAs have retired
+                    }
+                    __syncwarp();
+                }
+            }
+            if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_tc5_error, 3u); }
+        }
+    } else {
+        // ---------------- epilogue: warp w reads the lanes of tensor memory it may touch (32 * (w % 4) ...)
+        const int quarter = warp & 3;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+            const int acc = j & 1;
+            const int rt = tile % m_tiles, n0 = (tile / m_tiles) * kTileCols;
+            const int m0 = tile_row0[rt], M = offsets[tile_group[rt] + 1];      // the group's rows end before M
+            if (!mbar_wait(acc_full0 + 8 * acc, (j >> 1) & 1, abort_flag)) {
+                if (lane == 0) { *abort_flag = 1; atomicMax(&g_tc5_error, 4u); }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t lane_base = tmem_base + acc * kBN + ((uint32_t)(quarter * 32) << 16);
+            if (MODE == kSwiGLU) {
+#pragma unroll 1
+                for (int c = 0; c < kBN / 2; c += 32) {
+                    uint32_t gv[32], uv[32];
+                    tmem_ld32(lane_base + c, gv);
+                    tmem_ld32(lane_base + kBN / 2 + c, uv);
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g = __uint_as_float(gv[i]), u = __uint_as_float(uv[i]);
+                        f[i] = gated(g, u, inter);
+                    }
+                    if (row < M && n0 + c < inter) store32(out + (size_t)row * inter + n0 + c, f, inter - (n0 + c));
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < kBN; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_base + c, v);
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+                    if (row < M && n0 + c < N) store32(out + (size_t)row * N + n0 + c, f, N - (n0 + c));
+                }
+            }
+            // this warp has read its part of the accumulator: one of the four arrivals that free it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);
+        }
+    }
+    __syncwarp();
+    if (*abort_flag) {
+        // a role gave up: give copies that are still in flight time to land before this block's memory is reused
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+}
+
 // Row-major [rows, K] bfloat16 matrix, boxes of 128 rows x 64 columns, 128-byte swizzle, zero fill outside.
 int make_map(CUtensorMap* map, const void* base, int rows, int K) {
     EncodeTiledFn fn = encode_fn();
@@ -563,4 +710,46 @@ PB_EXPORT int pb_gemm_tcgen05(int mode, int out_dtype, const void* x, const void
     const int n_tiles = (N + kBN - 1) / kBN;
     if (out_dtype == PB_BF16) return launch<kPlain, bf16>(mx, mw, out, M, N, K, 0, m_tiles, n_tiles, stream);
     return launch<kPlain, float>(mx, mw, out, M, N, K, 0, m_tiles, n_tiles, stream);
+}
+
+
+// The grouped product (see gemm_tcgen05_grouped_kernel): x [P, K] rows sorted by group, W [n_groups * w_rows, K] the groups'
+// matrices one behind the other, bfloat16.  mode 0: w_rows = N, out [P, N] (out_dtype bfloat16 or float32) = x W[group]^T.
+// mode 1: w_rows = 2 * inter (gate rows, then up rows), out [P, inter] bfloat16 = the gated unit (limit <= 0: none).
+// offsets [n_groups + 1], tile_group / tile_row0 [max_row_tiles], meta[0] = tiles listed: device arrays.
+PB_EXPORT int pb_gemm_tcgen05_grouped(int mode, int out_dtype, const void* x, const void* w, void* out, int P, int N, int K,
+                                      int n_groups, const int* offsets, const int* tile_group, const int* tile_row0, const int* meta,
+                                      int max_row_tiles, float limit, float alpha, float shift, cudaStream_t stream) {
+    if (P <= 0 || max_row_tiles <= 0) return 0;
+    if (!pb_gemm_tcgen05_supported(mode, P, N, K) || n_groups <= 0 || (long long)n_groups * N > 0x7fffffff) return PB_ERR_BAD_SIZE;
+    if ((((uintptr_t)x | (uintptr_t)w) & 15) != 0) return PB_ERR_BAD_SIZE;
+    if (out_dtype != PB_BF16 && out_dtype != PB_F32) return PB_ERR_BAD_DTYPE;
+    CUtensorMap mx, mw;
+    int rc = make_map(&mx, x, P, K);
+    if (rc != 0) return rc;
+    rc = make_map(&mw, w, n_groups * N, K);
+    if (rc != 0) return rc;
+#define PB_GROUPED(MODE, OutT, INTER, NT)                                                                                         \
+    {                                                                                                                             \
+        static bool configured = false;                                                                                           \
+        if (!configured) {                                                                                                        \
+            cudaError_t ce = cudaFuncSetAttribute(gemm_tcgen05_grouped_kernel<MODE, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes); \
+            if (ce != cudaSuccess) return (int)ce;                                                                                \
+            configured = true;                                                                                                    \
+        }                                                                                                                         \
+        const long long tiles = (long long)max_row_tiles * (NT);                                                                  \
+        const int grid = (int)(tiles < sm_count() ? tiles : sm_count());                                                          \
+        gemm_tcgen05_grouped_kernel<MODE, OutT><<<grid, kThreads, kSmemBytes, stream>>>(mx, mw, (OutT*)out, N, K, INTER, NT, N,  \
+                                                                                        offsets, tile_group, tile_row0, meta);   \
+        return launch_status();                                                                                                   \
+    }
+    if (mode == kSwiGLU) {
+        if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
+        const GatedInter inter(N / 2, limit > 0.0f ? limit : __builtin_huge_valf(), alpha, shift);
+        PB_GROUPED(kSwiGLU, bf16, inter, ((int)inter + kBN / 2 - 1) / (kBN / 2))
+    }
+    const int n_tiles = (N + kBN - 1) / kBN;
+    if (out_dtype == PB_BF16) PB_GROUPED(kPlain, bf16, GatedInter(0), n_tiles)
+    PB_GROUPED(kPlain, float, GatedInter(0), n_tiles)
+#undef PB_GROUPED
 }

@@ -5,12 +5,15 @@
 //                   order), sorted [P] (the pairs, grouped by expert), and the list of row tiles: tile t covers rows
 //                   tile_row0[t] .. of expert tile_expert[t]; meta[0] = number of tiles.  One block; nothing returns to the host.
 //   moe_grouped     mode 0: act[sorted row] = gated(h[token] Wg[e]^T, h[token] Wu[e]^T)   (rows gathered by pair / top)
-//                   mode 1: y[pair] (float32) = act[sorted row] W_down[e]^T                (rows scattered back to their pair)
+//                   mode 1: y[sorted row] (float32) = act[sorted row] W_down[e]^T
 //                   mma.sync m16n8k16, bfloat16 operands, float32 accumulators; tiles of 128 rows x 64 output columns
 //                   (mode 0: 64 gate and the 64 up columns that go with them), K in steps of 64 through a three-stage cp.async
 //                   pipeline.  The grid has as many row tiles as the worst case needs; blocks beyond meta[0] return at once.
-//   moe_combine     out[n] = add[n] + sum over the slots, in their order, of weight[n, slot] * y[n * top + slot]; float32 sums,
-//                   one rounding.
+//   moe_combine     out[n] = add[n] + sum over the slots, in their order, of weight[n, slot] * y[place of pair n * top + slot];
+//                   float32 sums, one rounding.
+// Where the sizes allow it (contraction widths that are multiples of 8, as for every tcgen05 product of this library) the two
+// products run on the grouped form of the tcgen05 kernel instead (pb_gemm_tcgen05_grouped: TMA, tensor memory, the same tile
+// list), with the tokens' rows gathered into sorted order first (moe_gather_rows); PULSAR_MOE_TCGEN05=0 keeps mma.sync.
 // A row's result depends on that row and its expert's weights alone, so the order of the pairs inside an expert (which the
 // sort leaves to the atomics) does not show in the output.
 #include "mma_common.cuh"
@@ -23,8 +26,8 @@ constexpr int kBM = 128, kBN = 64, kBK = 64, kPad = 8, kStages = 3, kThreads = 2
 constexpr int kRow = kBK + kPad;                       // shared-memory row stride in elements (144 bytes: eight rows fall on eight different 16-byte columns of the banks)
 
 __global__ void moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int* __restrict__ offsets,
-                                int* __restrict__ sorted, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                                int* __restrict__ meta) {
+                                int* __restrict__ sorted, int* __restrict__ place, int* __restrict__ tile_expert,
+                                int* __restrict__ tile_row0, int* __restrict__ meta) {
     pdl_wait();
     extern __shared__ int sh[];                        // counts [E], cursor [E]
     int* counts = sh;
@@ -49,7 +52,21 @@ __global__ void moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int n_
         meta[0] = tiles;
     }
     __syncthreads();
-    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) sorted[atomicAdd(&cursor[ids[p]], 1)] = p;
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int at = atomicAdd(&cursor[ids[p]], 1);
+        sorted[at] = p;
+        place[p] = at;
+    }
+}
+
+// rows[at] = h[sorted[at] / top]: the tokens' rows in the order of the sorted pairs, 16 bytes a thread.
+__global__ void moe_gather_rows_kernel(const bf16* __restrict__ h, const int* __restrict__ sorted, bf16* __restrict__ rows, int width,
+                                       int top) {
+    pdl_wait();
+    const int at = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(sorted[at] / top) * width);
+    uint4* dst = reinterpret_cast<uint4*>(rows + (size_t)at * width);
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) dst[i] = src[i];
 }
 
 // MODE 0: gate/up with the gating; MODE 1: down.  Eight warps, four along the rows and two along the columns: a warp owns
@@ -166,7 +183,7 @@ moe_grouped_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
                     }
                 }
             } else {
-                float* dst = y_out + (size_t)sorted[row0 + r] * n_out;
+                float* dst = y_out + (size_t)(row0 + r) * n_out;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int col = n0 + warp_n * 32 + j * 8 + 2 * t;
@@ -180,13 +197,13 @@ moe_grouped_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const
         }
 }
 
-__global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const bf16* __restrict__ add,
-                                   bf16* __restrict__ out, int width, int top, size_t total) {
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
+                                   const bf16* __restrict__ add, bf16* __restrict__ out, int width, int top, size_t total) {
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t n = i / width, c = i % width;
         float sum = add ? __bfloat162float(add[i]) : 0.0f;
-        for (int slot = 0; slot < top; ++slot) sum = fmaf(weights[n * top + slot], y[(n * top + slot) * width + c], sum);
+        for (int slot = 0; slot < top; ++slot) sum = fmaf(weights[n * top + slot], y[(size_t)place[n * top + slot] * width + c], sum);
         out[i] = __float2bfloat16_rn(sum);
     }
 }
@@ -196,7 +213,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
 // Ints of the workspace that pb_moe_grouped needs for n tokens: offsets [E + 1], sorted [n * top], tile lists, meta.
 PB_EXPORT int pb_moe_grouped_workspace(int n, int top, int n_experts) {
     const int pairs = n * top, tiles = (pairs + kBM - 1) / kBM + n_experts;
-    return (n_experts + 1) + pairs + 2 * tiles + 4;
+    return (n_experts + 1) + 2 * pairs + 2 * tiles + 4;
 }
 
 // 1 when the grouped products take these sizes: contraction widths that are multiples of 8 (16-byte rows).
@@ -206,22 +223,47 @@ PB_EXPORT int pb_moe_grouped_supported(int width, int ff, int n_experts) {
 
 // h [n, width], w_gate_up [E, 2 ff, width], w_down [E, width, ff], add [n, width] or null, out [n, width]: bfloat16;
 // ids int32 [n, top], weights float32 [n, top]; act bfloat16 [n * top, ff] and y float32 [n * top, width] scratch;
-// work: int32 scratch of pb_moe_grouped_workspace(n, top, E) elements.  limit <= 0: no clamp.
+// work: int32 scratch of pb_moe_grouped_workspace(n, top, E) elements.  limit <= 0: no clamp.  gathered: bfloat16
+// [n * top, width] scratch for the tcgen05 form, or null for the mma.sync form.
+PB_EXPORT int pb_gemm_tcgen05_grouped(int mode, int out_dtype, const void* x, const void* w, void* out, int P, int N, int K,
+                                      int n_groups, const int* offsets, const int* tile_group, const int* tile_row0, const int* meta,
+                                      int max_row_tiles, float limit, float alpha, float shift, cudaStream_t stream);
+
 PB_EXPORT int pb_moe_grouped(const void* h, const void* w_gate_up, const void* w_down, const int* ids, const float* weights,
-                             const void* add, void* act, float* y, void* out, int* work, int n, int width, int ff, int n_experts,
-                             int top, float limit, float alpha, float shift, cudaStream_t stream) {
+                             const void* add, void* act, float* y, void* out, int* work, void* gathered, int n, int width, int ff,
+                             int n_experts, int top, float limit, float alpha, float shift, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (!pb_moe_grouped_supported(width, ff, n_experts) || top <= 0 || top > n_experts) return PB_ERR_BAD_SIZE;
     const int pairs = n * top, tiles = (pairs + kBM - 1) / kBM + n_experts;
     if (tiles > 0x7fffffff / 2 || (ff + kBN - 1) / kBN > 65535 || (width + kBN - 1) / kBN > 65535) return PB_ERR_TOO_LARGE;
     int* offsets = work;
     int* sorted = offsets + n_experts + 1;
-    int* tile_expert = sorted + pairs;
+    int* place = sorted + pairs;
+    int* tile_expert = place + pairs;
     int* tile_row0 = tile_expert + tiles;
     int* meta = tile_row0 + tiles;
     int rc = launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * n_experts, stream, ids, pairs, n_experts, offsets, sorted,
-                        tile_expert, tile_row0, meta);
+                        place, tile_expert, tile_row0, meta);
     if (rc != 0) return rc;
+    const size_t total = (size_t)n * width;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (gathered != nullptr) {
+        // the tcgen05 form: rows gathered into sorted order, then the two grouped products over the same tile list
+        int threads = width / 8;
+        threads = threads > 256 ? 256 : (threads + 31) / 32 * 32;
+        rc = launch_pdl(moe_gather_rows_kernel, dim3(pairs), dim3(threads), 0, stream, (const bf16*)h, (const int*)sorted, (bf16*)gathered,
+                        width, top);
+        if (rc != 0) return rc;
+        rc = pb_gemm_tcgen05_grouped(1, PB_BF16, gathered, w_gate_up, act, pairs, 2 * ff, width, n_experts, offsets, tile_expert, tile_row0,
+                                     meta, tiles, limit, alpha, shift, stream);
+        if (rc != 0) return rc;
+        rc = pb_gemm_tcgen05_grouped(0, PB_F32, act, w_down, y, pairs, width, ff, n_experts, offsets, tile_expert, tile_row0, meta, tiles,
+                                     0.0f, 1.0f, 0.0f, stream);
+        if (rc != 0) return rc;
+        return launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)y, (const int*)place, weights,
+                          (const bf16*)add, (bf16*)out, width, top, total);
+    }
     const GatedInter gating(ff, limit > 0.0f ? limit : __builtin_huge_valf(), alpha, shift);
     constexpr int smem0 = kStages * (kBM + 2 * kBN) * kRow * 2, smem1 = kStages * (kBM + kBN) * kRow * 2;
     static bool configured = false;
@@ -239,9 +281,6 @@ PB_EXPORT int pb_moe_grouped(const void* h, const void* w_gate_up, const void* w
                     (const bf16*)w_down, (const int*)offsets, (const int*)sorted, (const int*)tile_expert, (const int*)tile_row0,
                     (const int*)meta, (bf16*)nullptr, y, ff, width, top, gating);
     if (rc != 0) return rc;
-    const size_t total = (size_t)n * width;
-    size_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    return launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)y, weights, (const bf16*)add,
-                      (bf16*)out, width, top, total);
+    return launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)y, (const int*)place, weights,
+                      (const bf16*)add, (bf16*)out, width, top, total);
 }

@@ -113,7 +113,7 @@ _SIGNATURES = {
     "pb_moe_down": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "pb_moe_grouped_workspace": [_I, _I, _I],
     "pb_moe_grouped_supported": [_I, _I, _I],
-    "pb_moe_grouped": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
+    "pb_moe_grouped": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
 }
 _fns = {}
 # the entry points that launch kernels (the others answer questions on the host): what PULSAR_PROF=1 times
@@ -1310,6 +1310,9 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights
 # leaves the grouped products out.
 MOE_GROUPED = os.environ.get("PULSAR_MOE_GROUPED", "1") != "0"
 MOE_GROUPED_MIN = int(os.environ.get("PULSAR_MOE_GROUPED_MIN", "16") or 16)
+# The grouped products run on the grouped form of the tcgen05 kernel (TMA, tensor memory) when they are given scratch for the
+# gathered rows; PULSAR_MOE_TCGEN05=0 keeps them on mma.sync.
+MOE_TCGEN05 = os.environ.get("PULSAR_MOE_TCGEN05", "1") != "0"
 
 
 def moe_grouped_supported(dtype: torch.dtype, width: int, ff: int, n_experts: int) -> bool:
@@ -1322,11 +1325,14 @@ def moe_grouped_workspace(n: int, top: int, n_experts: int) -> int:
 
 
 def moe_grouped(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                add: Optional[torch.Tensor], act: torch.Tensor, y: torch.Tensor, out: torch.Tensor, work: torch.Tensor, gating) -> None:
+                add: Optional[torch.Tensor], act: torch.Tensor, y: torch.Tensor, out: torch.Tensor, work: torch.Tensor, gating,
+                gathered: Optional[torch.Tensor] = None) -> None:
     """What ``moe_gate_up`` and ``moe_down`` compute together, for steps of many tokens (bfloat16): pairs sorted by expert, the
     experts' products in tensor-core tiles, the weighted sum in the order of ``ids``.  ``act`` [N * top, ff] bfloat16, ``y``
-    [N * top, width] float32 and ``work`` (int32, ``moe_grouped_workspace`` elements) are scratch."""
-    _cuda(h, w_gate_up, w_down, ids, weights, add, act, y, out, work)
+    [N * top, width] float32 and ``work`` (int32, ``moe_grouped_workspace`` elements) are scratch.  With ``gathered``
+    (bfloat16 [N * top, width] scratch) the products run on the grouped tcgen05 kernel, else on mma.sync."""
+    _cuda(h, w_gate_up, w_down, ids, weights, add, act, y, out, work, gathered)
+    assert gathered is None or (gathered.dtype == torch.bfloat16 and gathered.shape == (h.shape[0] * ids.shape[1], h.shape[1]))
     n, width = h.shape
     e, two_ff, w2 = w_gate_up.shape
     ff, top = two_ff // 2, ids.shape[1]
@@ -1336,5 +1342,6 @@ def moe_grouped(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     assert out.shape == (n, width) and (add is None or (add.shape == out.shape and add.dtype == out.dtype))
     assert work.dtype == torch.int32 and work.numel() >= moe_grouped_workspace(n, top, e)
     limit, alpha, shift = gating if gating is not None else (0.0, 1.0, 0.0)
-    check(fn("pb_moe_grouped")(_p(h), _p(w_gate_up), _p(w_down), _p(ids), _p(weights), _p(add), _p(act), _p(y), _p(out), _p(work), n,
-                               width, ff, e, top, float(limit), float(alpha), float(shift), stream()), "moe_grouped", kernels=4)
+    check(fn("pb_moe_grouped")(_p(h), _p(w_gate_up), _p(w_down), _p(ids), _p(weights), _p(add), _p(act), _p(y), _p(out), _p(work),
+                               _p(gathered), n, width, ff, e, top, float(limit), float(alpha), float(shift), stream()), "moe_grouped",
+          kernels=4 if gathered is None else 5)

@@ -88,7 +88,8 @@ class MixtureOfExperts(FeedForward):
         if n > ops.MOE_GROUPED_MIN and ops.moe_grouped_supported(h.dtype, s.hidden, s.intermediate, self.n_experts):
             y = ctx.scratch("moe.y", (n * top, s.hidden), torch.float32)
             work = ctx.scratch("moe.work", (ops.moe_grouped_workspace(n, top, self.n_experts),), torch.int32)
-            ops.moe_grouped(h, self.w_gate_up, self.w_down, ids, weights, shared, act, y, out, work, self.gating)
+            gathered = ctx.scratch("moe.gathered", (n * top, s.hidden)) if ops.MOE_TCGEN05 else None
+            ops.moe_grouped(h, self.w_gate_up, self.w_down, ids, weights, shared, act, y, out, work, self.gating, gathered)
             return out
         ops.moe_gate_up(h, self.w_gate_up, ids, act, self.gating)
         ops.moe_down(act, self.w_down, ids, weights, shared, out)

@@ -528,8 +528,9 @@ def test_router_and_experts_against_their_formulas(dtype):
 
 
 @gpu
-@pytest.mark.parametrize("sizes", [(150, 40, 7, 3, 24), (37, 64, 3, 1, 72), (300, 72, 5, 5, 8)])
-def test_grouped_experts_equal_the_per_token_kernels(sizes):
+@pytest.mark.parametrize("tcgen05", [False, True])
+@pytest.mark.parametrize("sizes", [(150, 40, 7, 3, 24), (37, 64, 3, 1, 72), (300, 72, 5, 5, 8), (700, 320, 6, 2, 136)])
+def test_grouped_experts_equal_the_per_token_kernels(sizes, tcgen05):
     """Steps of many tokens sort their (token, expert) pairs by expert and run tensor-core tiles: against the same loops in
     float64, and against the kernels that steps of a few tokens take.  One expert gets more rows than a tile holds, one
     gets none."""
@@ -555,7 +556,9 @@ def test_grouped_experts_equal_the_per_token_kernels(sizes):
     out = torch.empty(n, width, dtype=dtype, device="cuda")
     work = torch.empty(ops.moe_grouped_workspace(n, top, E), dtype=torch.int32, device="cuda")
     assert ops.moe_grouped_supported(dtype, width, ff, E)
-    ops.moe_grouped(dev(h), dev(w_gu), dev(w_d), dev(ids), dev(wts), dev(add), act, y, out, work, gating)
+    gathered = torch.empty(n * top, width, dtype=dtype, device="cuda") if tcgen05 else None
+    ops.moe_grouped(dev(h), dev(w_gu), dev(w_d), dev(ids), dev(wts), dev(add), act, y, out, work, gating, gathered)
+    assert ops.gemm_tcgen05_error() == 0
     ref = torch.empty_like(out)
     act2 = torch.empty_like(act)
     ops.moe_gate_up(dev(h), dev(w_gu), dev(ids), act2, gating)
