@@ -13,9 +13,8 @@
 // gathered row by row through the block table (any page size) into XOR-swizzled tiles.  Tiles are aligned to
 // absolute key indices and taken in ascending order; a tile in which a row sees nothing leaves the row as it was.
 // Kept first keys (keep_first > 0: keys 0 .. keep_first - 1 stay visible below the window), a cap on the scaled score
-// (softcap > 0: softcap * tanh(score / softcap), tanhf in float32) and a sink per head (one more term exp(sinks[h]) in
-// the softmax's denominator) as in the CUDA-core kernels.
-// Sizes: (key width, value width) = (64, 64), (128, 128), (192, 128); everything else takes the CUDA-core kernels.
+// (softcap > 0: softcap * tanh(score / softcap) in float32, through ex2.approx like the softmax's exponentials) and a
+// sink per head (one more term exp(sinks[h]) in the softmax's denominator) as in the CUDA-core kernels.
 #include "mma_common.cuh"
 
 namespace {
@@ -30,6 +29,12 @@ __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// tanh(x) = 1 - 2 / (1 + e^(2x)) with the exponential from ex2.approx (relative error 2^-22) and an approximate division: the
+// absolute error stays below 3e-7, which in a capped score (cap * tanh) is a few units in the last place of the cap.
+__device__ __forceinline__ float tanh_ex2(float x) {
+    return 1.0f - __fdividef(2.0f, 1.0f + ex2(x * (2.0f * kLog2e)));
 }
 
 __device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
@@ -137,6 +142,7 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
     for (int i = 0; i < kNTiles; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
     const float sl2 = sh.scale * kLog2e;
+    const float cap_in = sh.softcap > 0.0f ? sh.scale / sh.softcap : 0.0f;
     const float slope2 = slopes ? slopes[head] * kLog2e : 0.0f;
     const int r0 = min(warp * 16 + g, rows - 1), r1 = min(warp * 16 + g + 8, rows - 1);
     const int pos0 = pos_first + r0, pos1 = pos_first + r1;
@@ -196,7 +202,7 @@ general_tc_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pool, 
                     float v = -INFINITY;
                     if (vis) {
                         if (sh.softcap > 0.0f)
-                            v = fmaf(sh.softcap * tanhf(sc[n][e] * sh.scale / sh.softcap), kLog2e, -slope2 * (float)(pos - key));
+                            v = fmaf(sh.softcap * tanh_ex2(sc[n][e] * cap_in), kLog2e, -slope2 * (float)(pos - key));
                         else
                             v = fmaf(sc[n][e], sl2, -slope2 * (float)(pos - key));
                     }
