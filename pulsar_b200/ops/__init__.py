@@ -1306,10 +1306,13 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights
 
 
 # Steps of more than MOE_GROUPED_MIN tokens (bfloat16) sort their (token, expert) pairs by expert on the device and run every
-# expert's rows through tensor-core tiles; fewer tokens read each chosen expert's weights per token.  PULSAR_MOE_GROUPED=0
-# leaves the grouped products out.
+# expert's rows through tensor-core tiles; fewer tokens read each chosen expert's weights per token.  The grouped form reads an
+# expert's weights once however many tokens chose it (TMA streams them), which already pays for a handful of single tokens:
+# 1.04 against 1.14 ms a step of 8 tokens at width 2,048 and 2.08 against 2.97 at 4,096 (32 experts, 4 a token); up to four
+# tokens rarely share an expert and keep the two per-token kernels.  PULSAR_MOE_GROUPED=0 leaves the grouped products out,
+# PULSAR_MOE_GROUPED_MIN=n moves the threshold.
 MOE_GROUPED = os.environ.get("PULSAR_MOE_GROUPED", "1") != "0"
-MOE_GROUPED_MIN = int(os.environ.get("PULSAR_MOE_GROUPED_MIN", "16") or 16)
+MOE_GROUPED_MIN = int(os.environ.get("PULSAR_MOE_GROUPED_MIN", "4") or 4)
 # The grouped products run on the grouped form of the tcgen05 kernel (TMA, tensor memory) when they are given scratch for the
 # gathered rows; PULSAR_MOE_TCGEN05=0 keeps them on mma.sync.
 MOE_TCGEN05 = os.environ.get("PULSAR_MOE_TCGEN05", "1") != "0"

@@ -25,10 +25,10 @@ class MixtureOfExperts(FeedForward):
     "down" (an expert's tensors are ``<prefix>e<i>.<name>``).
 
     The router's choice stays on the device: the kernels take the chosen ids as an array, so a step of single tokens can
-    be captured into a CUDA graph.  Steps of a few tokens read each chosen expert's weights per token
-    (``ops.moe_gate_up`` / ``ops.moe_down``: a warp per output element, fixed order of addition); larger steps in bfloat16
-    sort the (token, expert) pairs by expert on the device and run each expert's rows through tensor-core tiles
-    (``ops.moe_grouped``)."""
+    be captured into a CUDA graph.  Steps of up to ``ops.MOE_GROUPED_MIN`` tokens (and the float32 engine) read each chosen
+    expert's weights per token (``ops.moe_gate_up`` / ``ops.moe_down``: a warp per output element, fixed order of addition);
+    larger steps in bfloat16 sort the (token, expert) pairs by expert on the device and run each expert's rows through
+    tensor-core tiles, reading an expert's weights once (``ops.moe_grouped``)."""
 
     def __init__(self, spec: FeedForwardSpec, prefix: str, dtype: torch.dtype):
         self.spec, self.prefix, self.dtype = spec, prefix, dtype
