@@ -211,7 +211,8 @@ def topunex_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
     pairs = seqs * _window_pairs(n // seqs, start, z["window"], z["keep"])
     keys_read = seqs * min(start + n // seqs, z["window"] + z["keep"] + (n // seqs if phase == "prefill" else 0))
     attention = (L * (keys_read * G * 2 * d * 2 + n * H * d * (4 + 2)), L * 4.0 * H * d * pairs)
-    chosen = min(E, n * top)                             # experts whose weights a step of few tokens reads at most
+    chosen = n * top                                     # the per-token kernels read an expert's weights once per token that chose it
+    distinct = E * (1.0 - (1.0 - top / E) ** n)          # different experts that n tokens choose, on average: what the grouped products read
     work = {
         "paged_attention_general_tc": (attention[0], attention[1], "bf16 tensor"),
         "paged_attention_general_tiled": (attention[0], attention[1], "fp32 FMA"),
@@ -221,7 +222,7 @@ def topunex_work(z: dict, phase: str) -> Dict[str, Tuple[float, float, str]]:
         "post_norm_add_bias": (2 * L * n * w * (2 + 4 + 4 + 2), 0.0, ""),
         "glu_bias": (n * z["ff"] * (8 + 2), 0.0, ""),
         "moe_route": (moe_layers * (n * w * 2 + E * w * 4), 0.0, ""),
-        "moe_grouped": (moe_layers * (E * 3 * w * fe * 2 + n * w * 4 + n * top * (fe * 4 + w * 8)),
+        "moe_grouped": (moe_layers * (distinct * 3 * w * fe * 2 + n * w * 4 + n * top * (fe * 4 + w * 8)),
                         moe_layers * 2.0 * n * top * 3 * w * fe, "bf16 tensor"),
         "moe_gate_up": (moe_layers * (chosen * 2 * fe * w * 2 + n * w * 2), moe_layers * 4.0 * n * top * fe * w, "fp32 FMA"),
         "moe_down": (moe_layers * (chosen * fe * w * 2 + n * w * 4), moe_layers * 2.0 * n * top * fe * w, "fp32 FMA"),
