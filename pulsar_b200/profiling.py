@@ -92,7 +92,8 @@ def reset() -> None:
 
 def totals() -> Tuple[Dict[str, List[float]], Dict[str, List[float]]]:
     _drain()
-    return dict(_kernel_totals), dict(_host_totals)
+    # copies of the [count, time] pairs: what a caller keeps must not grow when later events are drained into the live ones
+    return {k: list(v) for k, v in _kernel_totals.items()}, {k: list(v) for k, v in _host_totals.items()}
 
 
 def report(file=None) -> None:
